@@ -1,0 +1,2 @@
+"""Module-path alias of ``gqa_decode_b200.fp8_utils``."""
+from gqa_decode_b200.fp8_utils import dequantize_kv_fp8, quantize_kv_fp8  # noqa: F401

@@ -1,0 +1,455 @@
+// extern "C" entry points of libgqa_decode_b200.so (declared in include/gqa_decode_b200.h).
+// Host-side work per call: argument checks, two tensor-map encodes, one (or two) launches.
+#include "../../include/gqa_decode_b200.h"
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "decode_kernel.cuh"
+#include "fp8_path.cuh"
+
+namespace gqa {
+
+// ------------------------------------------------------------------ workspace layout
+struct WorkspaceLayout {
+  size_t status_off, counters_off, info_off, lse_off, o_off, total;
+};
+static WorkspaceLayout layout_workspace(long long groups, long long slots, int G, int D) {
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  WorkspaceLayout w;
+  w.status_off = 0;
+  w.counters_off = 256;
+  w.info_off = up(w.counters_off + (size_t)groups * sizeof(int));
+  w.lse_off = up(w.info_off + (size_t)groups * sizeof(int2));
+  w.o_off = up(w.lse_off + (size_t)slots * G * sizeof(float));
+  w.total = up(w.o_off + (size_t)slots * G * D * sizeof(float));
+  return w;
+}
+
+static int sm_count_or(int fallback) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fallback;
+  }
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return fallback;
+  }
+  return n;
+}
+
+// ------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// View K (or V) as a row-major matrix [total_rows, row_bytes] and describe boxes of
+// [tile_rows x 128 bytes] with the 128-byte swizzle.  Rows past total_rows read as zero.
+static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, int head_dim,
+                       long long total_rows, int tile_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return GQA_ERR_DRIVER;
+  const bool fp8 = kv_dtype == GQA_DTYPE_E4M3;
+  const int esz = fp8 ? 1 : 2;
+  CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                               : (kv_dtype == GQA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)total_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)head_dim * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)tile_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : GQA_ERR_DRIVER;
+}
+
+// ------------------------------------------------------------------ dispatch
+static int tile_rows_for(int head_dim, int kv_dtype) {
+  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? 128 : 0;
+  if (head_dim == 128) return 64;
+  if (head_dim == 64) return 128;
+  return 0;
+}
+
+template <class Tr>
+static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodeParams prm,
+                         int num_ctas, cudaStream_t stream, bool separate_merge, long long groups) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  int smem_cap = 0;
+  e = cudaDeviceGetAttribute(&smem_cap, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (e != cudaSuccess) return (int)e;
+  const int grows = Tr::UPPER ? 16 : 8;
+  int nst = kMaxStages;
+  while (nst > 2 && decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows) > (size_t)smem_cap) --nst;
+  const size_t smem = decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows);
+  if (smem > (size_t)smem_cap) return GQA_ERR_SHAPE;
+  prm.num_stages = nst;
+  static std::atomic<unsigned long long> configured{0};  // bit per device (first 64 devices)
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    e = cudaFuncSetAttribute(decode_kernel<Tr>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_cap);
+    if (e != cudaSuccess) return (int)e;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  decode_kernel<Tr><<<num_ctas, kThreads, smem, stream>>>(tk, tv, prm);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (separate_merge) {
+    merge_groups_kernel<typename Tr::Q, Tr::D>
+        <<<(unsigned)groups, kConsumerThreads, 0, stream>>>(prm);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced) {
+  if (!a || !a->q || !a->k || !a->v || (!a->out && !a->out_f32) || !a->workspace) return GQA_ERR_ARG;
+  if (a->batch <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->max_seq_len <= 0 ||
+      a->total_rows <= 0 || a->num_splits < 0 || a->num_ctas < 0)
+    return GQA_ERR_ARG;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out) ||
+      !aligned16(a->out_f32) || !aligned16(a->workspace))
+    return GQA_ERR_ARG;
+  if (a->q_dtype != GQA_DTYPE_BF16 && a->q_dtype != GQA_DTYPE_FP16) return GQA_ERR_SHAPE;
+  const bool fp8 = a->kv_dtype == GQA_DTYPE_E4M3;
+  if (fp8 != want_fp8) return GQA_ERR_SHAPE;
+  if (!fp8 && a->kv_dtype != a->q_dtype) return GQA_ERR_SHAPE;
+  if (fp8 && (!a->k_scale || !a->v_scale)) return GQA_ERR_ARG;
+  if (a->num_q_heads % a->num_kv_heads) return GQA_ERR_SHAPE;
+  const int G = a->num_q_heads / a->num_kv_heads;
+  if (G > 16) return GQA_ERR_SHAPE;
+  const int D = a->head_dim;
+  const int tile = tile_rows_for(D, a->kv_dtype);
+  if (!tile) return GQA_ERR_SHAPE;
+  if (a->kv_layout != GQA_LAYOUT_PADDED && a->kv_layout != GQA_LAYOUT_PACKED) return GQA_ERR_ARG;
+  if (a->kv_layout == GQA_LAYOUT_PACKED && !a->seq_lens) return GQA_ERR_ARG;
+  if (a->total_rows >= (1ll << 31)) return GQA_ERR_LIMIT;  // TMA coordinates are 32-bit
+  const long long groups = (long long)a->batch * a->num_kv_heads;
+  if (a->kv_layout == GQA_LAYOUT_PADDED && groups * a->max_seq_len > a->total_rows)
+    return GQA_ERR_ARG;
+
+  const int num_ctas = a->num_ctas > 0 ? a->num_ctas : sm_count_or(0);
+  if (num_ctas <= 0) return (int)cudaErrorNoDevice;
+  const int splits = force_balanced ? 0 : a->num_splits;
+  const long long slots = max_slots(a->batch, a->num_kv_heads, num_ctas, splits);
+  const WorkspaceLayout w = layout_workspace(groups, slots, G, D);
+  if (a->workspace_bytes < w.total) return GQA_ERR_WORKSPACE;
+
+  CUtensorMap tk, tv;
+  int r = make_kv_map(&tk, a->k, a->kv_dtype, D, a->total_rows, tile);
+  if (r) return r;
+  r = make_kv_map(&tv, a->v, a->kv_dtype, D, a->total_rows, tile);
+  if (r) return r;
+
+  char* ws = static_cast<char*>(a->workspace);
+  DecodeParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.q = a->q;
+  prm.out = a->out;
+  prm.out_f32 = a->out_f32;
+  prm.out_lse = a->out_lse;
+  prm.k_scale = a->k_scale;
+  prm.v_scale = a->v_scale;
+  prm.status = reinterpret_cast<int*>(ws + w.status_off);
+  prm.counters = reinterpret_cast<int*>(ws + w.counters_off);
+  prm.group_info = reinterpret_cast<int2*>(ws + w.info_off);
+  prm.part_lse = reinterpret_cast<float*>(ws + w.lse_off);
+  prm.part_o = reinterpret_cast<float*>(ws + w.o_off);
+  prm.sched.seq_lens = a->seq_lens;
+  prm.sched.batch = a->batch;
+  prm.sched.num_kv_heads = a->num_kv_heads;
+  prm.sched.max_seq = a->max_seq_len;
+  prm.sched.tile_rows = tile;
+  prm.sched.num_ctas = num_ctas;
+  prm.sched.num_splits = splits;
+  prm.sched.layout = a->kv_layout;
+  prm.num_q_heads = a->num_q_heads;
+  prm.group = G;
+  const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)D);
+  prm.scale_log2 = scale * kLog2e;
+  const bool no_merge = (a->flags & GQA_FLAG_NO_MERGE) != 0;
+  if (no_merge && splits == 0) return GQA_ERR_ARG;
+  const bool separate = !no_merge && (a->flags & GQA_FLAG_SEPARATE_MERGE) != 0;
+  prm.fused_merge = (separate || no_merge) ? 0 : 1;
+  prm.no_merge = no_merge ? 1 : 0;
+
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  const bool upper = G > 8;
+  const bool bf = a->q_dtype == GQA_DTYPE_BF16;
+#define GQA_LAUNCH(...) \
+  return launch_decode<__VA_ARGS__>(tk, tv, prm, num_ctas, st, separate, groups)
+  if (fp8) {
+    if (bf) {
+      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true>);
+      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false>);
+    }
+    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true>);
+    GQA_LAUNCH(KvFp8Traits<__half, 128, false>);
+  }
+  if (D == 128) {
+    if (bf) {
+      if (upper) GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, true>);
+      GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, false>);
+    }
+    if (upper) GQA_LAUNCH(Kv16Traits<__half, 128, 64, true>);
+    GQA_LAUNCH(Kv16Traits<__half, 128, 64, false>);
+  }
+  if (bf) {
+    if (upper) GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 64, 128, true>);
+    GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 64, 128, false>);
+  }
+  if (upper) GQA_LAUNCH(Kv16Traits<__half, 64, 128, true>);
+  GQA_LAUNCH(Kv16Traits<__half, 64, 128, false>);
+#undef GQA_LAUNCH
+}
+
+// ------------------------------------------------------------------ generic merge
+template <typename Q>
+__global__ void merge_rows_kernel(const float* __restrict__ o_parts,
+                                  const float* __restrict__ lse_parts, int num_parts,
+                                  long long rows, int D, Q* out, float* out_f32, float* out_lse) {
+  const int D4 = D / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * D4) return;
+  const long long row = idx / D4;
+  const int d4 = (int)(idx % D4);
+  float mx = -INFINITY;
+  for (int p = 0; p < num_parts; ++p) mx = fmaxf(mx, lse_parts[(size_t)p * rows + row]);
+  const float ms = (mx == -INFINITY) ? 0.f : mx;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float wsum = 0.f;
+  for (int p = 0; p < num_parts; ++p) {
+    const float w = fast_exp2((lse_parts[(size_t)p * rows + row] - ms) * kLog2e);
+    const float4 o =
+        reinterpret_cast<const float4*>(o_parts + ((size_t)p * rows + row) * D)[d4];
+    acc.x += w * o.x;
+    acc.y += w * o.y;
+    acc.z += w * o.z;
+    acc.w += w * o.w;
+    wsum += w;
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  acc.x *= inv;
+  acc.y *= inv;
+  acc.z *= inv;
+  acc.w *= inv;
+  if (out) {
+    uint2 pk;
+    pk.x = Mma16<Q>::pack(acc.x, acc.y);
+    pk.y = Mma16<Q>::pack(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + row * D + 4 * d4) = pk;
+  }
+  if (out_f32) reinterpret_cast<float4*>(out_f32 + row * D)[d4] = acc;
+  if (out_lse && d4 == 0) out_lse[row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
+}
+
+// ------------------------------------------------------------------ scheduler dumps
+static __host__ __device__ void put_record(long long* rec, int cta, const Segment& s) {
+  rec[0] = cta;
+  rec[1] = s.b;
+  rec[2] = s.h;
+  rec[3] = s.row_begin;
+  rec[4] = s.row_end;
+  rec[5] = s.slot;
+  rec[6] = s.first_slot;
+  rec[7] = s.n_parts;
+  rec[8] = s.kv_row0;
+}
+
+__global__ void schedule_dump_kernel(SchedParams sp, long long* records, long long capacity,
+                                     unsigned long long* count) {
+  Walker wk;
+  wk.init_warp(sp, blockIdx.x);
+  if (threadIdx.x != 0) return;
+  Segment s;
+  while (wk.next(s)) {
+    const unsigned long long i = atomicAdd(count, 1ull);
+    if ((long long)i < capacity) put_record(records + 9 * i, blockIdx.x, s);
+  }
+}
+
+}  // namespace gqa
+
+using namespace gqa;
+
+extern "C" {
+
+const char* gqa_decode_version(void) { return "gqa_decode_b200 0.1 (sm_100a)"; }
+
+int gqa_decode_tile_rows(int32_t head_dim, int32_t kv_dtype) {
+  const int t = tile_rows_for(head_dim, kv_dtype);
+  return t ? t : GQA_ERR_SHAPE;
+}
+
+int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                               int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                               size_t* bytes) {
+  if (!bytes || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
+      num_splits < 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
+    return GQA_ERR_ARG;
+  // Without an explicit CTA count size for the SM count of the current device (or a
+  // generous bound when no device is visible, e.g. when sizing buffers on a host-only box).
+  const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(1024);
+  const long long groups = (long long)batch * num_kv_heads;
+  // a workspace sized for the balanced schedule also has to serve explicit splits and back
+  long long slots = max_slots(batch, num_kv_heads, ctas, num_splits);
+  const long long balanced = max_slots(batch, num_kv_heads, ctas, 0);
+  if (balanced > slots) slots = balanced;
+  *bytes = layout_workspace(groups, slots, num_q_heads / num_kv_heads, head_dim).total;
+  return 0;
+}
+
+int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                                size_t offsets[6]) {
+  if (!offsets || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
+      num_splits < 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
+    return GQA_ERR_ARG;
+  const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(0);
+  if (ctas <= 0) return (int)cudaErrorNoDevice;
+  const WorkspaceLayout w =
+      layout_workspace((long long)batch * num_kv_heads,
+                       max_slots(batch, num_kv_heads, ctas, num_splits),
+                       num_q_heads / num_kv_heads, head_dim);
+  offsets[0] = w.status_off;
+  offsets[1] = w.counters_off;
+  offsets[2] = w.info_off;
+  offsets[3] = w.lse_off;
+  offsets[4] = w.o_off;
+  offsets[5] = w.total;
+  return 0;
+}
+
+int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < 512) return GQA_ERR_ARG;
+  // status word + counters sit at the front; partial slots need no initialisation.
+  // The counter region is bounded by the first 256-byte boundary after them, but its
+  // size depends on the batch, so clear everything up to the partials conservatively:
+  // tickets are only ever non-zero inside a launch, so clearing more is harmless.
+  cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream));
+  return (int)e;
+}
+
+int gqa_decode_read_status(const void* workspace, void* stream, int32_t* status) {
+  if (!workspace || !status) return GQA_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(st);
+}
+
+int gqa_decode_attention(const gqa_decode_args_t* args) { return run_decode(args, false, false); }
+
+int gqa_decode_attention_persistent(const gqa_decode_args_t* args) {
+  return run_decode(args, false, true);
+}
+
+int gqa_decode_attention_fp8(const gqa_decode_args_t* args) { return run_decode(args, true, false); }
+
+int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num_parts,
+                       int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                       float* out_f32, float* out_lse, void* stream) {
+  if (!o_parts || !lse_parts || num_parts <= 0 || rows <= 0 || head_dim <= 0 || head_dim % 4 ||
+      (!out && !out_f32))
+    return GQA_ERR_ARG;
+  if (!aligned16(o_parts) || !aligned16(out) || !aligned16(out_f32)) return GQA_ERR_ARG;
+  if (out && out_dtype != GQA_DTYPE_BF16 && out_dtype != GQA_DTYPE_FP16) return GQA_ERR_SHAPE;
+  const long long work = rows * (head_dim / 4);
+  const int block = 128;
+  const unsigned grid = (unsigned)((work + block - 1) / block);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == GQA_DTYPE_FP16)
+    merge_rows_kernel<__half><<<grid, block, 0, st>>>(o_parts, lse_parts, num_parts, rows,
+                                                      head_dim, static_cast<__half*>(out),
+                                                      out_f32, out_lse);
+  else
+    merge_rows_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
+        o_parts, lse_parts, num_parts, rows, head_dim, static_cast<__nv_bfloat16*>(out), out_f32,
+        out_lse);
+  return (int)cudaGetLastError();
+}
+
+int gqa_select_num_splits(int32_t num_kv_heads, int32_t seq_len, int32_t block_seq,
+                          int32_t target_blocks_per_sm, int32_t num_sms) {
+  if (num_kv_heads <= 0 || block_seq <= 0 || target_blocks_per_sm <= 0 || num_sms <= 0)
+    return GQA_ERR_ARG;
+  // Same one-wave rule as the reference: grid = num_sms * min(target, shared-memory cap),
+  // splits = min(max(1, grid / Hkv), tiles).  The cap models two padded 16-bit tiles of
+  // head_dim 128 (row pad 8, 16-byte rounded) against 228 KB, minus one block of slack.
+  const long long tile = ((((long long)block_seq - 1) * (128 + 8) + 128) * 2 + 15) & ~15ll;
+  long long cap = (228ll * 1024) / (2 * tile) - 1;
+  if (cap < 1) cap = 1;
+  const long long per_sm = target_blocks_per_sm < cap ? target_blocks_per_sm : cap;
+  long long splits = (long long)num_sms * per_sm / num_kv_heads;
+  if (splits < 1) splits = 1;
+  long long tiles = ((long long)seq_len + block_seq - 1) / block_seq;
+  if (tiles < 1) tiles = 1;
+  return (int)(splits < tiles ? splits : tiles);
+}
+
+int64_t gqa_schedule_dump(const int32_t* seq_lens_host, int32_t batch, int32_t num_kv_heads,
+                          int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
+                          int32_t num_splits, int32_t kv_layout, int64_t* records,
+                          int64_t capacity) {
+  if (batch <= 0 || num_kv_heads <= 0 || max_seq_len <= 0 || tile_rows <= 0 || num_ctas <= 0 ||
+      num_splits < 0 || (capacity > 0 && !records))
+    return GQA_ERR_ARG;
+  SchedParams sp{seq_lens_host, batch, num_kv_heads, max_seq_len, tile_rows,
+                 num_ctas,      num_splits, kv_layout};
+  int64_t n = 0;
+  for (int c = 0; c < num_ctas; ++c) {
+    Walker wk;
+    wk.init_serial(sp, c);
+    Segment s;
+    while (wk.next(s)) {
+      if (n < capacity) put_record(reinterpret_cast<long long*>(records) + 9 * n, c, s);
+      ++n;
+    }
+  }
+  return n;
+}
+
+int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
+                             int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
+                             int32_t num_splits, int32_t kv_layout, int64_t* records,
+                             int64_t capacity, int64_t* count, void* stream) {
+  if (batch <= 0 || num_kv_heads <= 0 || max_seq_len <= 0 || tile_rows <= 0 || num_ctas <= 0 ||
+      num_splits < 0 || !records || !count)
+    return GQA_ERR_ARG;
+  SchedParams sp{seq_lens, batch, num_kv_heads, max_seq_len, tile_rows,
+                 num_ctas, num_splits, kv_layout};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int64_t), st);
+  if (e != cudaSuccess) return (int)e;
+  schedule_dump_kernel<<<num_ctas, 32, 0, st>>>(sp, reinterpret_cast<long long*>(records),
+                                               capacity,
+                                               reinterpret_cast<unsigned long long*>(count));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,549 @@
+// Persistent split-K decode-attention kernel for sm_100a.
+//
+// One CTA per SM.  Warp 4 is the producer: one elected lane walks the CTA's share of
+// the batch (schedule.cuh) and streams K and V tiles into a multi-stage shared-memory
+// ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers).
+// Warps 0-3 are consumers: each owns a quarter of every tile's keys, computes
+// S = Q K^T for the whole query group of the KV head with mma.sync (query heads
+// padded to the 16-row MMA tile), keeps an online softmax in registers and
+// accumulates O += P V, again on the tensor cores.  At the end of a segment the four
+// warps combine their states through shared memory and write either the final output
+// (the segment covered the whole (sequence, KV head) group) or one partial
+// (normalised O in fp32 + log-sum-exp) into the workspace; the CTA that completes a
+// group's last partial merges them (atomic ticket), so one launch does everything.
+//
+// Replaces the reference's DirectDecodeKernel / SplitKDecodeKernel /
+// DoubleBufferSplitKKernel / PersistentDecodeKernel (gqa_decode/gqa_decode.py:105-232,
+// :235-416, :1043-1320, :771-1040) and, through the in-kernel merge, its
+// ReductionKernel (:419-495).
+#pragma once
+#include "ptx.cuh"
+#include "schedule.cuh"
+
+namespace gqa {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxStages = 8;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+enum StatusBits : int {
+  kStatusOk = 0,
+  kStatusWaitFull = 1,    // a consumer gave up waiting for a tile
+  kStatusWaitEmpty = 2,   // the producer gave up waiting for a free stage
+  kStatusSmemAlign = 4,   // shared memory base not 1024-byte aligned
+};
+
+struct DecodeParams {
+  const void* q;        // [batch, Hq, D], 16-bit
+  void* out;            // [batch, Hq, D], same type as q (may be null if out_f32 is set)
+  float* out_f32;       // optional [batch, Hq, D] fp32 copy of the final output
+  float* out_lse;       // optional [batch, Hq] natural-log sum-exp of the scaled scores
+  const float* k_scale; // FP8 only: [batch * Hkv]
+  const float* v_scale; // FP8 only: [batch * Hkv]
+  float* part_o;        // workspace: [slots, G, D] fp32 normalised partial outputs
+  float* part_lse;      // workspace: [slots, G] natural-log sum-exp per partial
+  int* counters;        // workspace: [batch * Hkv] arrival tickets, zero between launches
+  int* status;          // workspace: one word, OR of StatusBits
+  int2* group_info;     // workspace: [batch * Hkv] {first_slot, n_parts}, written when the merge
+                        // runs as a separate kernel
+  SchedParams sched;
+  int num_q_heads;
+  int group;            // G = Hq / Hkv
+  float scale_log2;     // softmax scale * log2(e)
+  int fused_merge;      // 1: last-arriving CTA merges a group's partials in this launch
+  int no_merge;         // 1: every segment is written as a partial and nothing is merged
+  int num_stages;
+};
+
+template <int D>
+struct MergeSmem {
+  static constexpr int kStride = D + 8;  // floats; +8 keeps the float2 fragment stores conflict-free
+};
+
+__host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_stages, int head_dim,
+                                                    int group_rows) {
+  size_t b = 1024;  // alignment slack
+  b += (size_t)stage_bytes * num_stages;
+  b += (size_t)kConsumerWarps * group_rows * (head_dim + 8) * sizeof(float);
+  b += (size_t)kConsumerWarps * 16 * 2 * sizeof(float);
+  b += 2 * kMaxStages * sizeof(uint64_t);
+  b += 64;
+  return b;
+}
+
+// ---------------------------------------------------------------------------
+// Per-warp online-softmax state for a 16-row (padded) query group.
+// Thread (lane) owns rows r0 = lane/4 and r0+8, and columns 2*(lane%4)+{0,1} of
+// every 8-wide MMA tile.
+// ---------------------------------------------------------------------------
+template <int D, bool UPPER>
+struct WarpState {
+  float o[D / 8][4];
+  float m[2];
+  float l[2];
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// Online softmax over a 16-key block held as two S fragments; returns P packed for
+// the PV MMA (a0..a3) and rescales O when the running maximum moved.
+template <typename T16, int D, bool UPPER, bool PARTIAL>
+__device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPPER>& st,
+                                              uint32_t (&pa)[4], float scale_log2, int key0,
+                                              int valid, int lane) {
+  const int c = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const bool dead = PARTIAL && (key0 + 8 * j + 2 * c + e >= valid);
+      s[j][e] = dead ? -INFINITY : s[j][e] * scale_log2;
+      if (UPPER) s[j][2 + e] = dead ? -INFINITY : s[j][2 + e] * scale_log2;
+    }
+  float alpha[2] = {1.f, 1.f};
+  float p[2][4];
+#pragma unroll
+  for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
+    float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mnew = fmaxf(st.m[r], mx);
+    const float msafe = (mnew == -INFINITY) ? 0.f : mnew;
+    alpha[r] = fast_exp2(st.m[r] - msafe);
+    st.m[r] = mnew;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pv = fast_exp2(s[j][2 * r + e] - msafe);
+        p[j][2 * r + e] = pv;
+        sum += pv;
+      }
+    st.l[r] = st.l[r] * alpha[r] + sum;
+  }
+  const bool moved = alpha[0] != 1.f || (UPPER && alpha[1] != 1.f);
+  if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      st.o[i][0] *= alpha[0];
+      st.o[i][1] *= alpha[0];
+      if (UPPER) {
+        st.o[i][2] *= alpha[1];
+        st.o[i][3] *= alpha[1];
+      }
+    }
+  }
+  pa[0] = Mma16<T16>::pack(p[0][0], p[0][1]);
+  pa[2] = Mma16<T16>::pack(p[1][0], p[1][1]);
+  pa[1] = UPPER ? Mma16<T16>::pack(p[0][2], p[0][3]) : 0u;
+  pa[3] = UPPER ? Mma16<T16>::pack(p[1][2], p[1][3]) : 0u;
+}
+
+// ---------------------------------------------------------------------------
+// 16-bit K/V (bf16 or fp16): fragments come straight from the swizzled TMA tiles
+// with ldmatrix.  A tile holds TILE rows; a row of D 16-bit elements is stored as
+// D/64 separate boxes of [TILE x 128 B], each with the hardware 128-byte swizzle
+// (16-byte chunk index XOR (row & 7)), which makes every ldmatrix phase hit eight
+// different bank groups.
+// ---------------------------------------------------------------------------
+template <typename T16, int D, int TILE, bool UPPER, bool PARTIAL>
+__device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_base, int key0,
+                                                 int valid, const uint32_t (&qa)[D / 16][4],
+                                                 WarpState<D, UPPER>& st, float scale_log2,
+                                                 int lane) {
+  constexpr uint32_t kBoxBytes = TILE * 128;
+  float s[2][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  // S = Q K^T : B operand = K rows (n = key, k = d contiguous)
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ks += 2) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int key = key0 + 8 * j + (lane & 7);
+      const int chunk = 2 * ks + (lane >> 3);
+      const uint32_t addr = k_base + (chunk >> 3) * kBoxBytes + key * 128 +
+                            (((chunk & 7) ^ (key & 7)) << 4);
+      uint32_t r[4];
+      ldsm_x4(r, addr);
+      Mma16<T16>::run(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r[0], r[1]);
+      Mma16<T16>::run(s[j], qa[ks + 1][0], qa[ks + 1][1], qa[ks + 1][2], qa[ks + 1][3], r[2],
+                      r[3]);
+    }
+  }
+  uint32_t pa[4];
+  softmax_block<T16, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
+  // O += P V : B operand = V (k = key, n = d), transposed on load
+  const int c = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; nt += 2) {
+    const int key = key0 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int chunk = nt + (lane >> 4);
+    const uint32_t addr =
+        v_base + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+    uint32_t r[4];
+    ldsm_x4_trans(r, addr);
+    if (PARTIAL) {
+      // rows past the end of the sequence may hold anything (another head's data,
+      // padding, NaN patterns): force them to zero so that 0 * V stays 0.
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int k0 = key0 + 2 * c + (i & 1) * 8;
+        if (k0 >= valid) r[i] = 0u;
+        else if (k0 + 1 >= valid) r[i] &= 0x0000ffffu;
+      }
+    }
+    Mma16<T16>::run(st.o[nt], pa[0], pa[1], pa[2], pa[3], r[0], r[1]);
+    Mma16<T16>::run(st.o[nt + 1], pa[0], pa[1], pa[2], pa[3], r[2], r[3]);
+  }
+}
+
+template <typename T16_, int D_, int TILE_, bool UPPER_>
+struct Kv16Traits {
+  using Q = T16_;
+  static constexpr int D = D_;
+  static constexpr int TILE = TILE_;
+  static constexpr bool UPPER = UPPER_;
+  static constexpr bool kFp8 = false;
+  static constexpr int kBoxesPerTensor = D * 2 / 128;          // TMA boxes per K (or V) tile
+  static constexpr int kBoxBytes = TILE * 128;
+  static constexpr int kStageBytes = 2 * kBoxesPerTensor * kBoxBytes;
+  static constexpr int kBoxCols = 64;                          // elements per box row
+  struct Extra {};
+  __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, const Segment&) {}
+  template <bool PARTIAL>
+  __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
+                                                 int valid, const uint32_t (&qa)[D / 16][4],
+                                                 WarpState<D, UPPER>& st, float scale_log2,
+                                                 int lane, const Extra&) {
+    consume_block_16<Q, D, TILE, UPPER, PARTIAL>(k_base, v_base, key0, valid, qa, st, scale_log2,
+                                                 lane);
+  }
+  // Load the A fragments of Q for k-step ks: thread holds d = 16*ks + 2c + {0,1} and +8.
+  __device__ static __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const Q* row0,
+                                                const Q* row1, bool v0, bool v1, int c) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int d = 16 * ks + 2 * c;
+      qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(row0 + d) : 0u;
+      qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(row0 + d + 8) : 0u;
+      qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(row1 + d) : 0u;
+      qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(row1 + d + 8) : 0u;
+    }
+  }
+  // d index of accumulator element (n-tile nt, thread column c, element e).
+  __device__ static __forceinline__ int out_col(int nt, int c, int e) { return 8 * nt + 2 * c + e; }
+};
+
+// ---------------------------------------------------------------------------
+// Merge `n` partials of one group (rows = G query heads) and write the result.
+// Executed by the 128 consumer threads of the CTA that completed the group.
+// ---------------------------------------------------------------------------
+template <typename Q, int D>
+__device__ __forceinline__ void store_final(const DecodeParams& prm, long long out_row, int d4,
+                                            float4 v) {
+  if (prm.out) {
+    Q* o = reinterpret_cast<Q*>(prm.out) + out_row * D + 4 * d4;
+    uint2 pk;
+    pk.x = Mma16<Q>::pack(v.x, v.y);
+    pk.y = Mma16<Q>::pack(v.z, v.w);
+    *reinterpret_cast<uint2*>(o) = pk;
+  }
+  if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + out_row * D + 4 * d4) = v;
+}
+
+template <typename Q, int D>
+__device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_slot, int n,
+                                            long long out_row0, int tid) {
+  const int G = prm.group;
+  constexpr int D4 = D / 4;
+  for (int idx = tid; idx < G * D4; idx += kConsumerThreads) {
+    const int row = idx / D4, d4 = idx % D4;
+    float mx = -INFINITY;
+    for (int p = 0; p < n; ++p)
+      mx = fmaxf(mx, ld_cg_f32(prm.part_lse + (size_t)(first_slot + p) * G + row));
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    for (int p = 0; p < n; ++p) {
+      const size_t slot = (size_t)(first_slot + p);
+      const float w = fast_exp2((ld_cg_f32(prm.part_lse + slot * G + row) - ms) * kLog2e);
+      const float4 o = ld_cg_f32x4(
+          reinterpret_cast<const float4*>(prm.part_o + (slot * G + row) * D) + d4);
+      acc.x += w * o.x;
+      acc.y += w * o.y;
+      acc.z += w * o.z;
+      acc.w += w * o.w;
+      wsum += w;
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    store_final<Q, D>(prm, out_row0 + row, d4, acc);
+    if (d4 == 0 && prm.out_lse)
+      prm.out_lse[out_row0 + row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.
+// ---------------------------------------------------------------------------
+template <class Tr>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const DecodeParams prm) {
+  using Q = typename Tr::Q;
+  constexpr int D = Tr::D;
+  constexpr int TILE = Tr::TILE;
+  constexpr bool UPPER = Tr::UPPER;
+  constexpr int kRowsPerWarp = TILE / kConsumerWarps;
+  static_assert(kRowsPerWarp % 16 == 0, "each consumer warp works in 16-key blocks");
+  constexpr int kMoStride = MergeSmem<D>::kStride;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const int nst = prm.num_stages;
+  const int G = prm.group;
+  const int grows = UPPER ? 16 : 8;
+  uint8_t* stage0 = smem;
+  float* sm_o = reinterpret_cast<float*>(smem + (size_t)nst * Tr::kStageBytes);
+  float* sm_ml = sm_o + (size_t)kConsumerWarps * grows * kMoStride;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm_ml + kConsumerWarps * 16 * 2);
+  int* sm_flag = reinterpret_cast<int*>(bars + 2 * kMaxStages);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
+  const uint32_t stage_addr0 = smem_u32(stage0);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < nst; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kConsumerWarps);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  __syncthreads();
+
+  Walker wk;
+  wk.init_warp(prm.sched, blockIdx.x);
+  Segment seg;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer
+    if (lane != 0) return;
+    const uint64_t policy = l2_evict_first_policy();
+    uint32_t it = 0;
+    bool dead = false;
+    while (!dead && wk.next(seg)) {
+      const int rows = seg.row_end - seg.row_begin;
+      const int ntiles = (rows + TILE - 1) / TILE;
+      for (int t = 0; t < ntiles; ++t, ++it) {
+        const uint32_t s = it % nst, ph = (it / nst) & 1u;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) {
+          atomicOr(prm.status, kStatusWaitEmpty);
+          dead = true;
+          break;
+        }
+        const uint32_t fb = full0 + 8 * s;
+        mbar_expect_tx(fb, Tr::kStageBytes);
+        const long long row = seg.kv_row0 + seg.row_begin + (long long)t * TILE;
+        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes;
+        const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+#pragma unroll
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(kdst + bx * Tr::kBoxBytes, &tm_k, fb, bx * Tr::kBoxCols, (int)row, policy);
+#pragma unroll
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(vdst + bx * Tr::kBoxBytes, &tm_v, fb, bx * Tr::kBoxCols, (int)row, policy);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int r0 = lane >> 2, c = lane & 3;
+  const int Hq = prm.num_q_heads;
+
+  // Sequences without keys own no tiles in balanced mode: their outputs are zeros.
+  if (prm.sched.num_splits == 0 && prm.sched.seq_lens) {
+    for (int b = blockIdx.x; b < prm.sched.batch; b += gridDim.x) {
+      if (wk.len_of(b) > 0) continue;
+      for (int idx = tid; idx < Hq * (D / 4); idx += kConsumerThreads) {
+        const int row = idx / (D / 4), d4 = idx % (D / 4);
+        store_final<Q, D>(prm, (long long)b * Hq + row, d4, make_float4(0.f, 0.f, 0.f, 0.f));
+        if (d4 == 0 && prm.out_lse) prm.out_lse[(long long)b * Hq + row] = -INFINITY;
+      }
+      if (!prm.fused_merge)
+        for (int h = tid; h < prm.sched.num_kv_heads; h += kConsumerThreads)
+          prm.group_info[(long long)b * prm.sched.num_kv_heads + h] = make_int2(0, 1);
+    }
+  }
+
+  WarpState<D, UPPER> st;
+  uint32_t qa[D / 16][4];
+  typename Tr::Extra extra;
+  uint32_t it = 0;
+  bool dead = false;
+
+  while (wk.next(seg)) {
+    const long long out_row0 = (long long)seg.b * Hq + (long long)seg.h * G;
+    {
+      const Q* qbase = reinterpret_cast<const Q*>(prm.q) + out_row0 * D;
+      Tr::load_q(qa, qbase + (size_t)r0 * D, qbase + (size_t)(r0 + 8) * D, r0 < G,
+                 UPPER && (r0 + 8 < G), c);
+    }
+    Tr::begin_segment(extra, prm, seg);
+    st.reset();
+    const int rows = seg.row_end - seg.row_begin;
+    const int ntiles = (rows + TILE - 1) / TILE;
+    for (int t = 0; t < ntiles; ++t, ++it) {
+      const uint32_t s = it % nst, ph = (it / nst) & 1u;
+      if (!dead && !mbar_wait(full0 + 8 * s, ph)) {
+        if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
+        dead = true;
+      }
+      const int valid = min(TILE, rows - t * TILE);
+      const uint32_t kb = stage_addr0 + s * Tr::kStageBytes;
+      const uint32_t vb = kb + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+      if (!dead) {
+#pragma unroll
+        for (int sub = 0; sub < kRowsPerWarp / 16; ++sub) {
+          const int key0 = warp * kRowsPerWarp + sub * 16;
+          if (valid == TILE) {
+            Tr::template consume<false>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
+          } else if (key0 < valid) {
+            Tr::template consume<true>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+
+    // ---- combine the four warps' states -------------------------------------
+#pragma unroll
+    for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+    if (c == 0) {
+      sm_ml[(warp * 16 + r0) * 2 + 0] = st.m[0];
+      sm_ml[(warp * 16 + r0) * 2 + 1] = st.l[0];
+      if (UPPER) {
+        sm_ml[(warp * 16 + r0 + 8) * 2 + 0] = st.m[1];
+        sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = st.l[1];
+      }
+    }
+    bar_sync(1, kConsumerThreads);
+#pragma unroll
+    for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
+      const int row = r0 + 8 * r;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * 16 + row) * 2]);
+      const float Ms = (M == -INFINITY) ? 0.f : M;
+      float L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w)
+        L += sm_ml[(w * 16 + row) * 2 + 1] * fast_exp2(sm_ml[(w * 16 + row) * 2] - Ms);
+      const float f = L > 0.f ? fast_exp2(st.m[r] - Ms) / L : 0.f;
+      if (row < G) {
+        float* dst = sm_o + ((size_t)warp * grows + row) * kMoStride;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+          if constexpr (Tr::kFp8) {
+            dst[Tr::out_col(nt, c, 0)] = st.o[nt][2 * r] * f;
+            dst[Tr::out_col(nt, c, 1)] = st.o[nt][2 * r + 1] * f;
+          } else {
+            *reinterpret_cast<float2*>(dst + Tr::out_col(nt, c, 0)) =
+                make_float2(st.o[nt][2 * r] * f, st.o[nt][2 * r + 1] * f);
+          }
+        }
+      }
+    }
+    bar_sync(1, kConsumerThreads);
+    const bool direct = seg.n_parts == 1 && !prm.no_merge;
+    for (int idx = tid; idx < G * (D / 4); idx += kConsumerThreads) {
+      const int row = idx / (D / 4), d4 = idx % (D / 4);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(
+            sm_o + ((size_t)w * grows + row) * kMoStride + 4 * d4);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      if (direct) store_final<Q, D>(prm, out_row0 + row, d4, acc);
+      else
+        *reinterpret_cast<float4*>(prm.part_o + ((size_t)seg.slot * G + row) * D + 4 * d4) = acc;
+    }
+    if (tid < G) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * 16 + tid) * 2]);
+      const float Ms = (M == -INFINITY) ? 0.f : M;
+      float L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w)
+        L += sm_ml[(w * 16 + tid) * 2 + 1] * fast_exp2(sm_ml[(w * 16 + tid) * 2] - Ms);
+      const float lse = L > 0.f ? (Ms + fast_log2(L)) * kLn2 : -INFINITY;
+      if (direct) {
+        if (prm.out_lse) prm.out_lse[out_row0 + tid] = lse;
+      } else {
+        prm.part_lse[(size_t)seg.slot * G + tid] = lse;
+      }
+    }
+    if (!prm.fused_merge && tid == 0 && seg.slot == seg.first_slot)
+      prm.group_info[(long long)seg.b * prm.sched.num_kv_heads + seg.h] =
+          make_int2(seg.first_slot, seg.n_parts);
+    if (!direct && prm.fused_merge) {
+      __threadfence();
+      bar_sync(1, kConsumerThreads);
+      if (tid == 0) {
+        int* ctr = prm.counters + ((long long)seg.b * prm.sched.num_kv_heads + seg.h);
+        const int ticket = atomicAdd(ctr, 1);
+        const int last = ticket == seg.n_parts - 1;
+        if (last) *ctr = 0;  // every contributor has arrived: leave the counter clean
+        *sm_flag = last;
+      }
+      bar_sync(1, kConsumerThreads);
+      if (*sm_flag) {
+        __threadfence();
+        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid);
+      }
+    }
+    // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
+    bar_sync(1, kConsumerThreads);
+  }
+}
+
+// Second-kernel merge (one CTA of 128 threads per (sequence, KV head) group), used when
+// the in-kernel merge is switched off.
+template <typename Q, int D>
+__global__ void __launch_bounds__(kConsumerThreads)
+merge_groups_kernel(const DecodeParams prm) {
+  const long long g = blockIdx.x;
+  const int2 info = prm.group_info[g];
+  if (info.y <= 1) return;  // written directly by the decode kernel
+  const long long b = g / prm.sched.num_kv_heads, h = g % prm.sched.num_kv_heads;
+  merge_group<Q, D>(prm, info.x, info.y, b * prm.num_q_heads + h * prm.group, threadIdx.x);
+}
+
+}  // namespace gqa

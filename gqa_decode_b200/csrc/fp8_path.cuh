@@ -1,0 +1,148 @@
+// FP8-E4M3 K/V consumer for the persistent decode kernel.
+//
+// K and V tiles arrive as raw bytes ([TILE rows x 128 B], 128-byte swizzle).  Each
+// thread pulls the bytes its MMA fragments need with plain shared loads and
+// dequantises them in registers exactly as the reference's oracle does
+// (gqa_decode/fp8_utils.py:54-55): float32(code) * scale[head] rounded to nearest in
+// fp32, then rounded to nearest-even to the 16-bit MMA type.  The K scale is NOT
+// folded into the score: the oracle's bf16 rounding of each dequantised element is
+// part of the answer, and dropping it moves peaked softmax rows outside tolerance.
+// Replaces FP8DirectDecodeKernel / FP8SplitKDecodeKernel
+// (gqa_decode/gqa_decode.py:1454-1596, :1599-1803; dequant at :1565-1566, :1752-1753).
+//
+// Because the contraction index of an MMA may be permuted freely as long as A and B
+// agree, the d axis is permuted so that a thread's 16-byte shared load feeds four
+// k-steps of Q K^T, and the output columns of P V are permuted so that four
+// consecutive bytes of a V row feed four MMA tiles.  Q fragments and the epilogue
+// use the same permutations.
+#pragma once
+#include "decode_kernel.cuh"
+
+namespace gqa {
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// Two E4M3 codes (low byte first) -> two dequantised, rounded 16-bit values packed
+// for the MMA (low half = first code).
+template <typename T16>
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t two_codes, float scale) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)two_codes));
+  const float f0 = __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+  const float f1 = __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
+  return Mma16<T16>::pack(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
+}
+
+template <typename T16, int TILE, bool UPPER, bool PARTIAL>
+__device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_base, int key0,
+                                                  int valid, const uint32_t (&qa)[8][4],
+                                                  WarpState<128, UPPER>& st, float scale_log2,
+                                                  int lane, float k_scale, float v_scale) {
+  constexpr int D = 128;
+  const int n = lane >> 2, c = lane & 3;
+  float s[2][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int key = key0 + 8 * j + n;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 w = lds128(k_base + key * 128 + (((2 * c + i) ^ (key & 7)) << 4));
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int ks = 4 * i + t;
+        const uint32_t b0 = dequant_pair<T16>(ww[t] & 0xffffu, k_scale);
+        const uint32_t b1 = dequant_pair<T16>(ww[t] >> 16, k_scale);
+        Mma16<T16>::run(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      }
+    }
+  }
+  uint32_t pa[4];
+  softmax_block<T16, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int kk = key0 + 2 * c + (i & 1) + (i >> 1) * 8;
+      const uint32_t addr = v_base + kk * 128 + (((2 * q + (n >> 2)) ^ (kk & 7)) << 4) + 4 * (n & 3);
+      w[i] = lds32(addr);
+      if (PARTIAL && kk >= valid) w[i] = 0u;
+    }
+    const uint32_t p01a = prmt(w[0], w[1], 0x5140u), p01b = prmt(w[0], w[1], 0x7362u);
+    const uint32_t p23a = prmt(w[2], w[3], 0x5140u), p23b = prmt(w[2], w[3], 0x7362u);
+    const uint32_t lo[4] = {p01a & 0xffffu, p01a >> 16, p01b & 0xffffu, p01b >> 16};
+    const uint32_t hi[4] = {p23a & 0xffffu, p23a >> 16, p23b & 0xffffu, p23b >> 16};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t b0 = dequant_pair<T16>(lo[u], v_scale);
+      const uint32_t b1 = dequant_pair<T16>(hi[u], v_scale);
+      Mma16<T16>::run(st.o[4 * q + u], pa[0], pa[1], pa[2], pa[3], b0, b1);
+    }
+  }
+}
+
+template <typename T16_, int TILE_, bool UPPER_>
+struct KvFp8Traits {
+  using Q = T16_;
+  static constexpr int D = 128;
+  static constexpr int TILE = TILE_;
+  static constexpr bool UPPER = UPPER_;
+  static constexpr bool kFp8 = true;
+  static constexpr int kBoxesPerTensor = 1;
+  static constexpr int kBoxBytes = TILE * 128;
+  static constexpr int kStageBytes = 2 * kBoxBytes;
+  static constexpr int kBoxCols = 128;
+  struct Extra {
+    float ks, vs;
+  };
+  __device__ static __forceinline__ void begin_segment(Extra& e, const DecodeParams& prm,
+                                                       const Segment& seg) {
+    const long long g = (long long)seg.b * prm.sched.num_kv_heads + seg.h;
+    e.ks = __ldg(prm.k_scale + g);
+    e.vs = __ldg(prm.v_scale + g);
+  }
+  template <bool PARTIAL>
+  __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
+                                                 int valid, const uint32_t (&qa)[8][4],
+                                                 WarpState<128, UPPER>& st, float scale_log2,
+                                                 int lane, const Extra& e) {
+    consume_block_fp8<Q, TILE, UPPER, PARTIAL>(k_base, v_base, key0, valid, qa, st, scale_log2,
+                                               lane, e.ks, e.vs);
+  }
+  // k-step ks of thread column c covers d = 32c + 16(ks/4) + 4(ks%4) + {0,1 | 2,3}.
+  __device__ static __forceinline__ void load_q(uint32_t (&qa)[8][4], const Q* row0, const Q* row1,
+                                                bool v0, bool v1, int c) {
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int d = 32 * c + 16 * (ks >> 2) + 4 * (ks & 3);
+      qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(row0 + d) : 0u;
+      qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(row0 + d + 2) : 0u;
+      qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(row1 + d) : 0u;
+      qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(row1 + d + 2) : 0u;
+    }
+  }
+  // Accumulator tile nt = 4q + u, thread column c, element e holds d = 32q + 4(2c+e) + u.
+  __device__ static __forceinline__ int out_col(int nt, int c, int e) {
+    return 32 * (nt >> 2) + 4 * (2 * c + e) + (nt & 3);
+  }
+};
+
+}  // namespace gqa

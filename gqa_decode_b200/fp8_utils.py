@@ -1,0 +1,35 @@
+"""FP8-E4M3 KV-cache helpers with the data contract of the reference's
+``gqa_decode/fp8_utils.py``: one float32 scale per KV head, scale = amax / 448,
+codes = clamp(x / amax * 448) as ``float8_e4m3fn``; dequantisation is
+``float32(code) * scale`` rounded to bf16.  The decode kernels consume exactly this
+format (``gqa_decode_attention_fp8``)."""
+from __future__ import annotations
+
+import torch
+
+E4M3_MAX = 448.0
+
+
+def _quantize_one(x: torch.Tensor):
+    x32 = x.float()
+    amax = x32.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1e-12)
+    scale = (amax / E4M3_MAX).reshape(-1).float()
+    code = (x32 / amax * E4M3_MAX).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return code, scale
+
+
+def quantize_kv_fp8(k_bf16: torch.Tensor, v_bf16: torch.Tensor):
+    """Per-KV-head quantisation of ``[Hkv, S, D]`` caches (gqa_decode/fp8_utils.py:8-43).
+    Returns ``(k_fp8, v_fp8, k_scale[Hkv], v_scale[Hkv])``; multiply by the scale to
+    dequantise.  Runs as tensor ops on the inputs' device, off the decode path."""
+    k8, ks = _quantize_one(k_bf16)
+    v8, vs = _quantize_one(v_bf16)
+    return k8, v8, ks, vs
+
+
+def dequantize_kv_fp8(k_fp8, v_fp8, k_scale, v_scale):
+    """Back to bf16 (gqa_decode/fp8_utils.py:46-56), for comparisons against a 16-bit path."""
+    h = k_fp8.shape[0]
+    k = (k_fp8.float() * k_scale.view(h, 1, 1)).to(torch.bfloat16)
+    v = (v_fp8.float() * v_scale.view(h, 1, 1)).to(torch.bfloat16)
+    return k, v

@@ -1,0 +1,497 @@
+"""Host API of the B200 GQA decode-attention library.
+
+Mirrors the public surface of alityb/gqa-decode's ``gqa_decode/gqa_decode.py`` (same
+function names, keyword arguments and ``ValueError`` messages) and adds a batched /
+ragged entry point.  All attention math runs in the sm_100a kernels behind the C ABI
+(``include/gqa_decode_b200.h``); this module validates arguments, owns a reusable
+device workspace and fills in the argument struct.  PyTorch is used for device
+memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native
+
+DEFAULT_BLOCK_SEQ = 16
+DEFAULT_TARGET_BLOCKS_PER_SM = 16
+NUM_SMS_H100_SXM = 132
+SMEM_PAD = 8
+
+
+@dataclass(frozen=True)
+class GQADecodeConfig:
+    """Tuning knobs of the reference (gqa_decode/gqa_decode.py:29-33), kept for signature
+    compatibility.  The B200 kernels choose their own tile size and CTA count; the
+    fields only influence :func:`select_num_splits`, exactly as in the reference."""
+
+    block_seq: int = DEFAULT_BLOCK_SEQ
+    smem_pad: int = SMEM_PAD
+    target_blocks_per_sm: int = DEFAULT_TARGET_BLOCKS_PER_SM
+
+
+# ---------------------------------------------------------------------------
+# Functions of the reference API that are plain tensor algebra
+# ---------------------------------------------------------------------------
+
+def reference_gqa_decode(q, k_cache, v_cache, num_kv_heads=None):
+    """Exact float32 attention in PyTorch ops, on whatever device the tensors live on.
+
+    Part of the reference's public API (gqa_decode/gqa_decode.py:36-66) and what
+    ``backend="torch"`` selects.  It is never chosen automatically: the CUDA kernels
+    have no fallback.
+    """
+    if q.dim() != 2 or k_cache.dim() != 3 or v_cache.dim() != 3:
+        raise ValueError(
+            "Expected q=(num_q_heads, head_dim), k/v=(num_kv_heads, seq_len, head_dim)"
+        )
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have identical shapes")
+    num_q_heads, head_dim = q.shape
+    kv_heads, _, kv_head_dim = k_cache.shape
+    if kv_head_dim != head_dim:
+        raise ValueError("Q/K/V head_dim mismatch")
+    if num_kv_heads is None:
+        num_kv_heads = kv_heads
+    if num_kv_heads != kv_heads:
+        raise ValueError("num_kv_heads must match k_cache.shape[0]")
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    owner = torch.arange(num_q_heads, device=q.device) // (num_q_heads // num_kv_heads)
+    logits = torch.einsum("hd,hsd->hs", q.float(), k_cache.float()[owner]) * head_dim ** -0.5
+    weights = torch.softmax(logits, dim=-1)
+    return torch.einsum("hs,hsd->hd", weights, v_cache.float()[owner]).to(dtype=q.dtype)
+
+
+def select_num_splits(
+    num_kv_heads: int,
+    seq_len: int,
+    block_seq: int = DEFAULT_BLOCK_SEQ,
+    target_blocks_per_sm: int = DEFAULT_TARGET_BLOCKS_PER_SM,
+    num_sms: int = NUM_SMS_H100_SXM,
+) -> int:
+    """The reference's one-wave split heuristic (gqa_decode/gqa_decode.py:80-102),
+    evaluated by the native library.  The B200 kernels do not need it (their default is
+    the balanced persistent schedule); it is kept because callers use it to pick an
+    explicit ``num_splits``."""
+    if num_kv_heads <= 0:
+        raise ValueError("num_kv_heads must be positive")
+    r = _native.load().gqa_select_num_splits(
+        num_kv_heads, seq_len, block_seq, target_blocks_per_sm, num_sms)
+    if r < 0:
+        _native.check(r, "gqa_select_num_splits")
+    return r
+
+
+def reduce_partials(partial_out, partial_max, partial_sum, num_q_heads, num_splits, head_dim):
+    """Combine split-K partials given in the reference's three-tensor format
+    (gqa_decode/gqa_decode.py:647-669): un-normalised accumulators ``[Hq*splits, D]`` and
+    running max / sum broadcast over ``D`` (column 0 is read).  Tensor ops on the
+    tensors' own device; this is what ``reduction="python"`` runs."""
+    out_dtype = partial_out.dtype
+    m = partial_max[:, 0].reshape(num_q_heads, num_splits)
+    l = partial_sum[:, 0].reshape(num_q_heads, num_splits)
+    top = m.max(dim=1, keepdim=True).values
+    w = torch.exp(m - top)
+    denom = (l * w).sum(dim=1, keepdim=True)
+    acc = partial_out.reshape(num_q_heads, num_splits, head_dim).float()
+    return (torch.einsum("qsd,qs->qd", acc, w) / denom).to(out_dtype)
+
+
+# ---------------------------------------------------------------------------
+# Workspace
+# ---------------------------------------------------------------------------
+
+_DTYPE_CODE = {torch.bfloat16: _native.DTYPE_BF16, torch.float16: _native.DTYPE_FP16}
+_workspaces: dict = {}
+
+
+def workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_splits=0, num_ctas=0) -> int:
+    n = ctypes.c_size_t(0)
+    _native.check(
+        _native.load().gqa_decode_workspace_bytes(
+            batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, ctypes.byref(n)),
+        "gqa_decode_workspace_bytes")
+    return n.value
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A zero-initialised scratch tensor per device, grown on demand and reused by
+    every call on that device (calls that overlap on different streams must pass their
+    own ``workspace=``)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def read_status(workspace: Optional[torch.Tensor] = None, device=None) -> int:
+    """Synchronise and return the kernels' status word (0 = ok; non-zero = a bounded
+    wait inside a kernel expired and the result of that call is invalid)."""
+    if workspace is None:
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        workspace = _workspace(dev, 512)
+    st = ctypes.c_int32(0)
+    _native.check(
+        _native.load().gqa_decode_read_status(
+            workspace.data_ptr(), torch.cuda.current_stream(workspace.device).cuda_stream,
+            ctypes.byref(st)),
+        "gqa_decode_read_status")
+    return st.value
+
+
+# ---------------------------------------------------------------------------
+# Batched entry (new) — everything else is a thin wrapper over it
+# ---------------------------------------------------------------------------
+
+def gqa_decode_attention_batched(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    layout: str = "padded",
+    k_scale: Optional[torch.Tensor] = None,
+    v_scale: Optional[torch.Tensor] = None,
+    num_splits: Optional[int] = None,
+    num_ctas: int = 0,
+    separate_merge: bool = False,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    return_lse: bool = False,
+    return_f32: bool = False,
+    workspace: Optional[torch.Tensor] = None,
+    max_seq_len: Optional[int] = None,
+    num_kv_heads: Optional[int] = None,
+    _entry: str = "auto",
+    _no_merge: bool = False,
+):
+    """One decode step for a batch of sequences with individual KV lengths.
+
+    q: ``[B, Hq, D]`` bf16/fp16.
+    layout="padded": k/v ``[B, Hkv, Smax, D]``; ``seq_lens`` int32 ``[B]`` on the device
+      (``None`` = all ``Smax``).
+    layout="packed": k/v ``[Hkv * sum(len), D]`` where sequence ``b`` stores its
+      ``[Hkv, len_b, D]`` slab after all earlier sequences; ``seq_lens``, ``num_kv_heads``
+      and ``max_seq_len`` (a bound on every length) are required.
+    k/v dtype is q's dtype, or ``float8_e4m3fn`` with ``k_scale``/``v_scale`` fp32
+    ``[B, Hkv]`` (per sequence and KV head, the reference's fp8_utils scheme).
+    num_splits: ``None`` = balanced persistent schedule; ``K`` = K partials per
+      (sequence, KV head).
+    Returns out ``[B, Hq, D]`` (q dtype), plus float32 output and/or natural-log LSE
+    ``[B, Hq]`` when asked.  A sequence of length 0 yields zeros and LSE = -inf.
+    """
+    lib = _native.load()
+    if q.dim() != 3:
+        raise ValueError("Expected q=(batch, num_q_heads, head_dim)")
+    if q.device.type != "cuda" or k_cache.device.type != "cuda" or v_cache.device.type != "cuda":
+        raise ValueError("All tensors must be CUDA tensors")
+    if q.dtype not in _DTYPE_CODE:
+        raise ValueError("Only fp16 and bf16 are supported")
+    fp8 = k_cache.dtype == torch.float8_e4m3fn
+    if fp8:
+        if v_cache.dtype != torch.float8_e4m3fn:
+            raise ValueError("K/V must be float8_e4m3fn")
+    elif k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("Q/K/V dtypes must match")
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous")
+    batch, num_q_heads, head_dim = q.shape
+    if layout == "padded":
+        if k_cache.dim() != 4:
+            raise ValueError("padded layout expects k/v=(batch, num_kv_heads, max_seq, head_dim)")
+        kb, num_kv_heads, smax, kv_head_dim = k_cache.shape
+        if kb != batch:
+            raise ValueError("Q and K/V batch sizes differ")
+        total_rows = batch * num_kv_heads * smax
+        code_layout = _native.LAYOUT_PADDED
+    elif layout == "packed":
+        if k_cache.dim() != 2 or seq_lens is None or max_seq_len is None or num_kv_heads is None:
+            raise ValueError(
+                "packed layout expects k/v=(num_kv_heads*sum(len), head_dim), seq_lens, "
+                "max_seq_len and num_kv_heads")
+        total_rows, kv_head_dim = k_cache.shape
+        smax = int(max_seq_len)
+        code_layout = _native.LAYOUT_PACKED
+    else:
+        raise ValueError("layout must be 'padded' or 'packed'")
+    if kv_head_dim != head_dim:
+        raise ValueError("Q/K/V head_dim mismatch")
+    if fp8:
+        if k_scale is None or v_scale is None:
+            raise ValueError("Scales must be [num_kv_heads]")
+        if k_scale.numel() != batch * num_kv_heads or v_scale.numel() != batch * num_kv_heads:
+            raise ValueError("Scales must be [num_kv_heads]")
+        if k_scale.dtype != torch.float32 or v_scale.dtype != torch.float32:
+            raise ValueError("Scales must be float32")
+        k_scale = k_scale.contiguous()
+        v_scale = v_scale.contiguous()
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    if num_q_heads // num_kv_heads > 16:
+        raise ValueError("group size must be in [1, 16]")
+    if head_dim not in ((128,) if fp8 else (64, 128)):
+        raise ValueError("head_dim must be 64 or 128 (128 for FP8)")
+    if seq_lens is not None:
+        if seq_lens.dtype != torch.int32 or seq_lens.device != q.device or seq_lens.numel() != batch:
+            raise ValueError("seq_lens must be an int32 CUDA tensor of shape [batch]")
+        seq_lens = seq_lens.contiguous()
+    splits = 0 if num_splits is None else int(num_splits)
+    if splits < 0:
+        raise ValueError("num_splits must be positive")
+
+    dev = q.device
+    need = workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas)
+    ws = workspace if workspace is not None else _workspace(dev, need)
+    if ws.numel() * ws.element_size() < need:
+        raise ValueError(f"workspace too small: need {need} bytes")
+    if out is None:
+        out = torch.empty_like(q)
+    out_f32 = torch.empty(q.shape, dtype=torch.float32, device=dev) if return_f32 else None
+    out_lse = torch.empty(q.shape[:2], dtype=torch.float32, device=dev) if return_lse else None
+
+    a = _native.DecodeArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+    a.out_f32 = out_f32.data_ptr() if out_f32 is not None else None
+    a.out_lse = out_lse.data_ptr() if out_lse is not None else None
+    a.seq_lens = seq_lens.data_ptr() if seq_lens is not None else None
+    a.k_scale = k_scale.data_ptr() if fp8 else None
+    a.v_scale = v_scale.data_ptr() if fp8 else None
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = batch, num_q_heads, num_kv_heads, head_dim
+    a.max_seq_len, a.total_rows = smax, total_rows
+    a.q_dtype = _DTYPE_CODE[q.dtype]
+    a.kv_dtype = _native.DTYPE_E4M3 if fp8 else a.q_dtype
+    a.kv_layout = code_layout
+    a.num_splits, a.num_ctas = splits, num_ctas
+    a.flags = (_native.FLAG_SEPARATE_MERGE if separate_merge else 0) | (
+        _native.FLAG_NO_MERGE if _no_merge else 0)
+    a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    if fp8:
+        fn = lib.gqa_decode_attention_fp8
+    elif _entry == "persistent":
+        fn = lib.gqa_decode_attention_persistent
+    else:
+        fn = lib.gqa_decode_attention
+    with torch.cuda.device(dev):
+        _native.check(fn(ctypes.byref(a)), fn.__name__ if hasattr(fn, "__name__") else "gqa_decode")
+    extras = tuple(t for t in (out_f32, out_lse) if t is not None)
+    return (out, *extras) if extras else out
+
+
+def _partials_for_python_reduction(q, k, v, k_scale, v_scale, splits):
+    """Run the kernel with GQA_FLAG_NO_MERGE and return its partials re-expressed in the
+    reference's three-tensor format for :func:`reduce_partials`: acc = normalised O,
+    max = LSE, sum = 1 (exp(LSE_i - M) * O_i summed over i, divided by the sum of
+    exp(LSE_i - M), is the same merge)."""
+    num_q_heads, head_dim = q.shape
+    num_kv_heads = k.shape[0]
+    g = num_q_heads // num_kv_heads
+    need = workspace_bytes(1, num_q_heads, num_kv_heads, head_dim, splits, 0)
+    ws = _workspace(q.device, need)
+    gqa_decode_attention_batched(
+        q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), None,
+        k_scale=None if k_scale is None else k_scale.view(1, -1),
+        v_scale=None if v_scale is None else v_scale.view(1, -1),
+        num_splits=splits, workspace=ws, _no_merge=True)
+    off = (ctypes.c_size_t * 6)()
+    _native.check(
+        _native.load().gqa_decode_workspace_layout(
+            1, num_q_heads, num_kv_heads, head_dim, splits, 0, off),
+        "gqa_decode_workspace_layout")
+    slots = num_kv_heads * splits
+    lse = ws[off[3]: off[3] + slots * g * 4].view(torch.float32).view(num_kv_heads, splits, g)
+    o = ws[off[4]: off[4] + slots * g * head_dim * 4].view(torch.float32).view(
+        num_kv_heads, splits, g, head_dim)
+    # reference row index = q_head * splits + split (gqa_decode/gqa_decode.py:392-393)
+    acc = o.permute(0, 2, 1, 3).reshape(num_q_heads * splits, head_dim).to(q.dtype)
+    mx = lse.permute(0, 2, 1).reshape(num_q_heads * splits, 1).expand(-1, head_dim)
+    one = torch.ones_like(mx)
+    return acc, mx, one
+
+
+# ---------------------------------------------------------------------------
+# Reference-compatible single-sequence entries
+# ---------------------------------------------------------------------------
+
+def gqa_decode_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    num_splits: Optional[int] = None,
+    config: Optional[GQADecodeConfig] = None,
+    backend: str = "cute",
+    reduction: str = "fused",
+) -> torch.Tensor:
+    """Drop-in for gqa_decode/gqa_decode.py:672-762.
+
+    ``backend``: "cute" (the reference's name for its kernel path) and "cuda" both run
+    the sm_100a kernels; "torch" is the caller's explicit request for
+    :func:`reference_gqa_decode`.  ``num_splits=None`` uses the balanced persistent
+    schedule; an integer forces that many partials per KV head.  ``reduction="fused"``
+    merges inside the launch, ``"python"`` merges the partials with tensor ops
+    (:func:`reduce_partials`).
+    """
+    if q.dim() != 2 or k_cache.dim() != 3 or v_cache.dim() != 3:
+        raise ValueError(
+            "Expected q=(num_q_heads, head_dim), k/v=(num_kv_heads, seq_len, head_dim)"
+        )
+    if q.device.type != "cuda" or k_cache.device.type != "cuda" or v_cache.device.type != "cuda":
+        raise ValueError("All tensors must be CUDA tensors")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("Only fp16 and bf16 are supported")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("Q/K/V dtypes must match")
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous")
+    num_q_heads, head_dim = q.shape
+    num_kv_heads, _, kv_head_dim = k_cache.shape
+    if kv_head_dim != head_dim:
+        raise ValueError("Q/K/V head_dim mismatch")
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    if backend not in {"cute", "cuda", "torch"}:
+        raise ValueError("backend must be one of {'cute', 'torch'}")
+    if reduction not in {"fused", "python"}:
+        raise ValueError("reduction must be one of {'fused', 'python'}")
+    if backend == "torch":
+        return reference_gqa_decode(q, k_cache, v_cache, num_kv_heads=num_kv_heads)
+    if reduction == "python":
+        cfg = config or GQADecodeConfig()
+        splits = num_splits if num_splits is not None else select_num_splits(
+            num_kv_heads, k_cache.shape[1], cfg.block_seq, cfg.target_blocks_per_sm)
+        acc, mx, one = _partials_for_python_reduction(q, k_cache, v_cache, None, None, splits)
+        return reduce_partials(acc, mx, one, num_q_heads, splits, head_dim)
+    out = gqa_decode_attention_batched(
+        q.unsqueeze(0), k_cache.unsqueeze(0), v_cache.unsqueeze(0), None, num_splits=num_splits)
+    return out.squeeze(0)
+
+
+def gqa_decode_attention_persistent(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    config: Optional[GQADecodeConfig] = None,
+) -> torch.Tensor:
+    """Drop-in for gqa_decode/gqa_decode.py:1365-1446: one persistent CTA per SM, each
+    walking an equal contiguous share of the (KV head, tile) list."""
+    if q.dim() != 2 or k_cache.dim() != 3 or v_cache.dim() != 3:
+        raise ValueError(
+            "Expected q=(num_q_heads, head_dim), k/v=(num_kv_heads, seq_len, head_dim)"
+        )
+    if q.device.type != "cuda":
+        raise ValueError("All tensors must be CUDA tensors")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("Only fp16 and bf16 are supported")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("Q/K/V dtypes must match")
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous")
+    num_q_heads, head_dim = q.shape
+    num_kv_heads, _, kv_head_dim = k_cache.shape
+    if kv_head_dim != head_dim:
+        raise ValueError("Q/K/V head_dim mismatch")
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    out = gqa_decode_attention_batched(
+        q.unsqueeze(0), k_cache.unsqueeze(0), v_cache.unsqueeze(0), None, _entry="persistent")
+    return out.squeeze(0)
+
+
+def gqa_decode_attention_fp8(
+    q: torch.Tensor,
+    k_fp8: torch.Tensor,
+    v_fp8: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    *,
+    num_splits: Optional[int] = None,
+    config: Optional[GQADecodeConfig] = None,
+    reduction: str = "fused",
+) -> torch.Tensor:
+    """Drop-in for gqa_decode/gqa_decode.py:1900-2010: E4M3 K/V ``[Hkv, S, D]`` with one
+    float32 scale per KV head; K/V are dequantised in registers, with the rounding of
+    ``fp8_utils.dequantize_kv_fp8``."""
+    if q.dim() != 2 or k_fp8.dim() != 3 or v_fp8.dim() != 3:
+        raise ValueError(
+            "Expected q=(num_q_heads, head_dim), k/v=(num_kv_heads, seq_len, head_dim)"
+        )
+    if q.device.type != "cuda":
+        raise ValueError("All tensors must be CUDA tensors")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("Q must be fp16 or bf16")
+    if k_fp8.dtype != torch.float8_e4m3fn or v_fp8.dtype != torch.float8_e4m3fn:
+        raise ValueError("K/V must be float8_e4m3fn")
+    if k_fp8.shape != v_fp8.shape:
+        raise ValueError("k and v must have the same shape")
+    if not (q.is_contiguous() and k_fp8.is_contiguous() and v_fp8.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous")
+    num_q_heads, head_dim = q.shape
+    num_kv_heads, _, kv_head_dim = k_fp8.shape
+    if kv_head_dim != head_dim:
+        raise ValueError("Q/K/V head_dim mismatch")
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    if k_scale.shape != (num_kv_heads,) or v_scale.shape != (num_kv_heads,):
+        raise ValueError("Scales must be [num_kv_heads]")
+    if reduction not in {"fused", "python"}:
+        raise ValueError("reduction must be one of {'fused', 'python'}")
+    ks = k_scale.to(device=q.device, dtype=torch.float32)
+    vs = v_scale.to(device=q.device, dtype=torch.float32)
+    if reduction == "python":
+        cfg = config or GQADecodeConfig()
+        splits = num_splits if num_splits is not None else select_num_splits(
+            num_kv_heads, k_fp8.shape[1], cfg.block_seq, cfg.target_blocks_per_sm)
+        acc, mx, one = _partials_for_python_reduction(q, k_fp8, v_fp8, ks, vs, splits)
+        return reduce_partials(acc, mx, one, num_q_heads, splits, head_dim)
+    out = gqa_decode_attention_batched(
+        q.unsqueeze(0), k_fp8.unsqueeze(0), v_fp8.unsqueeze(0), None,
+        k_scale=ks.view(1, -1), v_scale=vs.view(1, -1), num_splits=num_splits)
+    return out.squeeze(0)
+
+
+def merge_partials(
+    o_parts: torch.Tensor,
+    lse_parts: torch.Tensor,
+    out_dtype: torch.dtype = torch.bfloat16,
+    return_lse: bool = False,
+):
+    """LSE-weighted merge of normalised partials on the GPU (``gqa_merge_partials``).
+    o_parts ``[P, R, D]`` float32, lse_parts ``[P, R]`` float32 (natural log; -inf = empty).
+    Used for partials gathered from sequence shards on other GPUs."""
+    if o_parts.dim() != 3 or lse_parts.shape != o_parts.shape[:2]:
+        raise ValueError("Expected o_parts=(parts, rows, head_dim), lse_parts=(parts, rows)")
+    if o_parts.dtype != torch.float32 or lse_parts.dtype != torch.float32:
+        raise ValueError("partials must be float32")
+    if o_parts.device.type != "cuda":
+        raise ValueError("All tensors must be CUDA tensors")
+    o_parts, lse_parts = o_parts.contiguous(), lse_parts.contiguous()
+    parts, rows, d = o_parts.shape
+    f32 = out_dtype == torch.float32
+    out = torch.empty(rows, d, dtype=out_dtype, device=o_parts.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=o_parts.device) if return_lse else None
+    with torch.cuda.device(o_parts.device):
+        _native.check(
+            _native.load().gqa_merge_partials(
+                o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, d,
+                None if f32 else out.data_ptr(), _DTYPE_CODE.get(out_dtype, 0),
+                out.data_ptr() if f32 else None, lse.data_ptr() if lse is not None else None,
+                torch.cuda.current_stream(o_parts.device).cuda_stream),
+            "gqa_merge_partials")
+    return (out, lse) if return_lse else out

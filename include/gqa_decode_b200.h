@@ -1,0 +1,164 @@
+/*
+ * C ABI of the B200 (sm_100a) GQA decode-attention library.
+ *
+ * This is the boundary a binding of alityb/gqa-decode would call instead of its
+ * CuTe-DSL JIT callables.  Every function takes plain pointers and sizes, returns an
+ * int (0 = ok, negative = bad argument (GQA_ERR_*), positive = cudaError_t), never
+ * throws, never exits, never allocates or frees device memory unless its comment says
+ * so, and enqueues its work on the CUDA stream it is given without synchronising.
+ * Device pointers must be 16-byte aligned and refer to the device that is current on
+ * the calling thread.
+ *
+ * Citations `gqa_decode/...py:N` name the reference interface each entry replaces.
+ */
+#ifndef GQA_DECODE_B200_H_
+#define GQA_DECODE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define GQA_DTYPE_BF16 0
+#define GQA_DTYPE_FP16 1
+#define GQA_DTYPE_E4M3 2
+
+/* K/V memory layouts (rows of head_dim elements, every (sequence, KV head) slab contiguous
+ * exactly like the reference's [Hkv, S, D] tensors, gqa_decode/gqa_decode.py:44) */
+#define GQA_LAYOUT_PADDED 0 /* [batch, Hkv, max_seq_len, D]; batch = 1 is the reference layout */
+#define GQA_LAYOUT_PACKED 1 /* sequence b holds [Hkv, len_b, D], sequences back to back */
+
+/* flags */
+#define GQA_FLAG_SEPARATE_MERGE 1 /* run the merge as a second kernel instead of in-kernel */
+#define GQA_FLAG_NO_MERGE 2       /* explicit splits only: write every partial, merge nothing */
+
+/* errors */
+#define GQA_ERR_ARG (-1)       /* null pointer, non-positive size, misaligned pointer */
+#define GQA_ERR_SHAPE (-2)     /* unsupported head_dim / group size / dtype combination */
+#define GQA_ERR_WORKSPACE (-3) /* workspace too small */
+#define GQA_ERR_DRIVER (-4)    /* cuTensorMapEncodeTiled unavailable or failed */
+#define GQA_ERR_LIMIT (-5)     /* size beyond a documented maximum */
+
+/*
+ * One decode step over a batch.  Replaces the argument lists of
+ * gqa_decode_attention (gqa_decode/gqa_decode.py:672-681),
+ * gqa_decode_attention_fp8 (:1900-1910) and gqa_decode_attention_persistent
+ * (:1365-1371); batch/seq_lens/layout are additions (the reference is single-sequence).
+ */
+typedef struct gqa_decode_args {
+  const void* q;            /* [batch, num_q_heads, head_dim], q_dtype (bf16 or fp16) */
+  const void* k;            /* K cache, kv_dtype, layout above */
+  const void* v;            /* V cache, same shape and type as k */
+  void* out;                /* [batch, num_q_heads, head_dim] in q_dtype; may be NULL if out_f32 given */
+  float* out_f32;           /* optional fp32 copy of the output (sequence-shard partials) */
+  float* out_lse;           /* optional [batch, num_q_heads] natural-log sum-exp of the scaled scores */
+  const int32_t* seq_lens;  /* device [batch] KV lengths, or NULL: every sequence has max_seq_len keys */
+  const float* k_scale;     /* E4M3 only: device [batch * num_kv_heads] dequantisation scales */
+  const float* v_scale;     /* E4M3 only: same */
+  int32_t batch;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;         /* 64 or 128 (E4M3: 128) */
+  int32_t max_seq_len;      /* rows per head slab (padded layout); bound on every length */
+  int64_t total_rows;       /* rows of the whole K (= V) allocation, viewed as [rows, head_dim] */
+  int32_t q_dtype;          /* GQA_DTYPE_BF16 | GQA_DTYPE_FP16 */
+  int32_t kv_dtype;         /* q_dtype, or GQA_DTYPE_E4M3 */
+  int32_t kv_layout;        /* GQA_LAYOUT_* */
+  int32_t num_splits;       /* 0: balanced persistent schedule; K>0: K partials per (sequence, KV head) */
+  int32_t num_ctas;         /* 0: one CTA per SM */
+  int32_t flags;            /* GQA_FLAG_* */
+  float softmax_scale;      /* 0: head_dim ** -0.5 (gqa_decode/gqa_decode.py:60) */
+  void* workspace;          /* device scratch of gqa_decode_workspace_bytes(); reusable across calls */
+  size_t workspace_bytes;
+  void* stream;             /* cudaStream_t */
+} gqa_decode_args_t;
+
+/* Bytes of device scratch a launch with these sizes needs (partials, tickets, status). */
+int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                               int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                               size_t* bytes);
+
+/*
+ * Byte offsets inside a workspace of the same arguments: offsets[0] status word,
+ * [1] tickets, [2] group table, [3] partial log-sum-exp [slots, G] fp32,
+ * [4] partial outputs [slots, G, head_dim] fp32, [5] total bytes.  With explicit splits
+ * K, slot = (sequence * Hkv + kv_head) * K + split.  Lets a caller that asked for
+ * GQA_FLAG_NO_MERGE read the partials (the reference's reduction="python" path,
+ * gqa_decode/gqa_decode.py:753-756).
+ */
+int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                                size_t offsets[6]);
+
+/* Zero the ticket counters and the status word.  Call once after allocating a workspace
+ * (kernels leave both clean) and after any launch that reported a non-zero status. */
+int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Copy the status word back (synchronises the stream): 0 = ok, else OR of
+ * 1 (consumer wait expired), 2 (producer wait expired), 4 (shared-memory misalignment). */
+int gqa_decode_read_status(const void* workspace, void* stream, int32_t* status);
+
+/* bf16 / fp16 K and V.  Replaces gqa_decode_attention, gqa_decode/gqa_decode.py:672-762
+ * (DirectDecodeKernel :105, SplitKDecodeKernel :235, DoubleBufferSplitKKernel :1043,
+ * ReductionKernel :419). */
+int gqa_decode_attention(const gqa_decode_args_t* args);
+
+/* Same kernel, always the balanced persistent schedule.  Replaces
+ * gqa_decode_attention_persistent, gqa_decode/gqa_decode.py:1365-1446
+ * (PersistentDecodeKernel :771). */
+int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
+
+/* E4M3 K and V with per-(sequence, KV head) fp32 scales.  Replaces
+ * gqa_decode_attention_fp8, gqa_decode/gqa_decode.py:1900-2010
+ * (FP8DirectDecodeKernel :1454, FP8SplitKDecodeKernel :1599). */
+int gqa_decode_attention_fp8(const gqa_decode_args_t* args);
+
+/*
+ * LSE-weighted merge of normalised partials.  o_parts [num_parts, rows, head_dim] fp32,
+ * lse_parts [num_parts, rows] (natural log, -inf = empty partial).  Writes
+ * out [rows, head_dim] in out_dtype (may be NULL), out_f32 and out_lse (optional).
+ * Replaces ReductionKernel / reduce_partials, gqa_decode/gqa_decode.py:419-495, :647-669;
+ * also merges the (O, LSE) partials of sequence shards gathered from other GPUs.
+ */
+int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num_parts,
+                       int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                       float* out_f32, float* out_lse, void* stream);
+
+/* One-wave split heuristic of the reference, gqa_decode/gqa_decode.py:80-102.
+ * Returns the split count (>= 1) or a negative error. */
+int gqa_select_num_splits(int32_t num_kv_heads, int32_t seq_len, int32_t block_seq,
+                          int32_t target_blocks_per_sm, int32_t num_sms);
+
+/* Keys per pipeline tile the kernels use for this configuration (schedule granularity). */
+int gqa_decode_tile_rows(int32_t head_dim, int32_t kv_dtype);
+
+/*
+ * Host-side replay of the device scheduler, for inspection and tests: fills up to
+ * `capacity` records of 9 int64 each {cta, seq, kv_head, row_begin, row_end, slot,
+ * first_slot, n_parts, kv_row0} for the launch described by the arguments
+ * (seq_lens is a HOST array here, or NULL).  Returns the number of segments, or a
+ * negative error.  No GPU needed.
+ */
+int64_t gqa_schedule_dump(const int32_t* seq_lens_host, int32_t batch, int32_t num_kv_heads,
+                          int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
+                          int32_t num_splits, int32_t kv_layout, int64_t* records,
+                          int64_t capacity);
+
+/* Same records produced by the device-side scheduler (warp-cooperative set-up) running on
+ * the GPU; seq_lens is a DEVICE array, records a DEVICE buffer of capacity*9 int64,
+ * count a DEVICE int64.  For tests. */
+int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
+                             int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
+                             int32_t num_splits, int32_t kv_layout, int64_t* records,
+                             int64_t capacity, int64_t* count, void* stream);
+
+/* Library version string. */
+const char* gqa_decode_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GQA_DECODE_B200_H_ */

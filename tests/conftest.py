@@ -1,0 +1,21 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """The C-ABI shared library, built on demand (nvcc cross-compiles without a GPU)."""
+    from gqa_decode_b200 import _native, build
+
+    build.build()
+    return _native.load()

@@ -1,0 +1,86 @@
+"""Host-side mirror of the reference interface: same names, same ValueErrors, same
+answers for the helper functions (checked against the golden fixtures)."""
+import numpy as np
+import pytest
+import torch
+
+import gqa_decode
+import gqa_decode.fp8_utils
+import gqa_decode.gqa_decode
+import gqa_decode_b200 as G
+from gqa_decode_b200 import fp8_utils
+from tests.golden_io import bits_equal, from_bits, load
+
+
+def test_public_names():
+    for n in ["GQADecodeConfig", "gqa_decode_attention", "gqa_decode_attention_fp8",
+              "gqa_decode_attention_persistent", "reduce_partials", "reference_gqa_decode",
+              "select_num_splits"]:
+        assert hasattr(gqa_decode, n) and hasattr(gqa_decode.gqa_decode, n)
+    assert hasattr(gqa_decode.fp8_utils, "quantize_kv_fp8")
+    assert hasattr(gqa_decode.fp8_utils, "dequantize_kv_fp8")
+    cfg = G.GQADecodeConfig()
+    assert (cfg.block_seq, cfg.smem_pad, cfg.target_blocks_per_sm) == (16, 8, 16)
+    with pytest.raises(Exception):
+        cfg.block_seq = 4  # frozen, like the reference's dataclass
+
+
+def test_select_num_splits_table(native_lib):
+    for hkv, s, bs, tb, sms, want in load("select_num_splits.npz")["table"]:
+        assert G.select_num_splits(int(hkv), int(s), int(bs), int(tb), int(sms)) == int(want)
+    with pytest.raises(ValueError, match="num_kv_heads must be positive"):
+        G.select_num_splits(0, 10)
+
+
+def test_reduce_partials_matches_reference():
+    z = load("reduce_partials.npz")
+    hq, splits, d = (int(x) for x in z["dims"])
+    out = G.reduce_partials(from_bits(z["acc"], torch.bfloat16), torch.from_numpy(z["mx"]),
+                            torch.from_numpy(z["sm"]), hq, splits, d)
+    assert bits_equal(out, from_bits(z["out"], torch.bfloat16))
+
+
+def test_fp8_utils_match_reference():
+    z = load("fp8.npz")
+    bf, f8 = torch.bfloat16, torch.float8_e4m3fn
+    k8, v8, ks, vs = fp8_utils.quantize_kv_fp8(from_bits(z["k"], bf), from_bits(z["v"], bf))
+    assert bits_equal(k8, from_bits(z["k8"], f8)) and bits_equal(v8, from_bits(z["v8"], f8))
+    assert np.array_equal(ks.numpy(), z["k_scale"]) and np.array_equal(vs.numpy(), z["v_scale"])
+    kd, vd = fp8_utils.dequantize_kv_fp8(k8, v8, ks, vs)
+    assert bits_equal(kd, from_bits(z["k_deq"], bf)) and bits_equal(vd, from_bits(z["v_deq"], bf))
+
+
+def test_torch_entry_matches_reference_output():
+    z = load("attention_small.npz")
+    q, k, v, ref = (from_bits(z[f"b_{n}"], torch.bfloat16) for n in ("q", "k", "v", "out"))
+    assert bits_equal(G.reference_gqa_decode(q, k, v), ref)
+
+
+def test_validation_errors_cpu():
+    bf = torch.bfloat16
+    q, k, v = torch.zeros(8, 64, dtype=bf), torch.zeros(2, 5, 64, dtype=bf), torch.zeros(2, 5, 64, dtype=bf)
+    with pytest.raises(ValueError, match="Expected q="):
+        G.gqa_decode_attention(q[0], k, v)
+    with pytest.raises(ValueError, match="All tensors must be CUDA tensors"):
+        G.gqa_decode_attention(q, k, v)  # CPU tensors are refused: there is no CPU path
+    with pytest.raises(ValueError, match="All tensors must be CUDA tensors"):
+        G.gqa_decode_attention_persistent(q, k, v)
+    with pytest.raises(ValueError, match="All tensors must be CUDA tensors"):
+        G.gqa_decode_attention_fp8(q, k, v, torch.ones(2), torch.ones(2))
+    with pytest.raises(ValueError, match="identical shapes"):
+        G.reference_gqa_decode(q, k, v[:, :4])
+    with pytest.raises(ValueError, match="head_dim mismatch"):
+        G.reference_gqa_decode(q[:, :32], k, v)
+    with pytest.raises(ValueError, match="divisible"):
+        G.reference_gqa_decode(q[:7], k, v)
+    with pytest.raises(ValueError, match="num_kv_heads must match"):
+        G.reference_gqa_decode(q, k, v, num_kv_heads=4)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from gqa_decode_b200 import _native
+
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setattr(_native, "lib_path", lambda: str(tmp_path / "absent.so"))
+    with pytest.raises(RuntimeError, match="no non-CUDA fallback"):
+        _native.load()

@@ -1,0 +1,98 @@
+"""Host replay of the device scheduler (gqa_schedule_dump): every key of every
+(sequence, KV head) group is covered exactly once, partial slots never collide, and
+each group's bookkeeping (first_slot, n_parts) agrees across the CTAs that share it."""
+import numpy as np
+import pytest
+
+
+def dump(lib, lens, hkv, max_seq, tile, ctas, splits, layout):
+    cap = 1 << 16
+    rec = np.zeros((cap, 9), dtype=np.int64)
+    arr = None if lens is None else np.asarray(lens, dtype=np.int32)
+    batch = len(lens) if lens is not None else 3
+    n = lib.gqa_schedule_dump(None if arr is None else arr.ctypes.data, batch, hkv, max_seq, tile,
+                              ctas, splits, layout, rec.ctypes.data, cap)
+    assert 0 <= n <= cap
+    return rec[:n], batch
+
+
+def check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout):
+    lens = [max_seq] * batch if lens is None else [min(l, max_seq) if layout == 0 else l for l in lens]
+    covered = {}
+    slots = set()
+    info = {}
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    for cta, b, h, r0, r1, slot, first, nparts, row0 in rec:
+        assert 0 <= cta < ctas and 0 <= b < batch and 0 <= h < hkv
+        assert r0 % tile == 0 and r0 <= r1 <= lens[b]
+        assert slot not in slots
+        slots.add(slot)
+        bound = batch * hkv * splits if splits else batch * hkv + ctas
+        assert 0 <= slot < bound
+        assert first <= slot < first + nparts
+        g = (b, h)
+        assert info.setdefault(g, (first, nparts)) == (first, nparts)
+        covered.setdefault(g, []).append((r0, r1))
+        want_row0 = (b * hkv + h) * max_seq if layout == 0 else cu[b] * hkv + h * lens[b]
+        assert row0 == want_row0
+    for b in range(batch):
+        for h in range(hkv):
+            segs = sorted(s for s in covered.get((b, h), []) if s[0] != s[1] or splits)
+            if lens[b] == 0 and not splits:
+                assert not segs
+                continue
+            pos = 0
+            for r0, r1 in segs:
+                if r0 == r1:
+                    continue  # empty chunk of an explicit split
+                assert r0 == pos
+                pos = r1
+            assert pos == lens[b]
+            first, nparts = info[(b, h)]
+            assert len(covered[(b, h)]) == nparts
+    if not splits:  # balanced: per-CTA tile counts differ by at most one
+        per = np.zeros(ctas, dtype=np.int64)
+        for cta, b, h, r0, r1, *_ in rec:
+            per[cta] += -(-(r1 - r0) // tile)
+        assert per.max() - per.min() <= 1
+
+
+CASES = [
+    ([1, 7, 32768, 500, 12345], 8, 32768, 64, 148, 0),
+    ([1, 7, 32768, 500, 12345], 8, 32768, 64, 148, 5),
+    ([16384], 8, 16384, 64, 148, 0),
+    ([16384], 8, 16384, 64, 148, 264),
+    ([131072], 8, 131072, 64, 148, 0),
+    ([0, 5, 0, 0, 64, 65, 0], 4, 128, 64, 148, 0),
+    ([0, 5, 0, 0, 64, 65, 0], 4, 128, 64, 7, 3),
+    ([3], 1, 3, 128, 148, 0),
+    (None, 2, 1000, 128, 5, 0),
+    (None, 2, 1000, 128, 5, 1),
+    (list(range(1, 80)), 2, 100, 64, 148, 0),
+    ([8192] * 64, 8, 8192, 64, 148, 0),
+    ([8192] * 64, 1, 8192, 128, 148, 0),
+]
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("lens,hkv,max_seq,tile,ctas,splits", CASES)
+def test_schedule_invariants(native_lib, lens, hkv, max_seq, tile, ctas, splits, layout):
+    if layout == 1 and lens is None:
+        pytest.skip("packed layout needs lengths")
+    rec, batch = dump(native_lib, lens, hkv, max_seq, tile, ctas, splits, layout)
+    check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout)
+
+
+def test_schedule_random(native_lib):
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        batch = int(rng.integers(1, 40))
+        hkv = int(rng.choice([1, 2, 4, 8]))
+        max_seq = int(rng.integers(1, 3000))
+        lens = rng.integers(0, max_seq + 1, batch).tolist()
+        tile = int(rng.choice([64, 128]))
+        ctas = int(rng.integers(1, 200))
+        splits = int(rng.choice([0, 0, 1, 3, 17]))
+        layout = int(rng.integers(0, 2))
+        rec, _ = dump(native_lib, lens, hkv, max_seq, tile, ctas, splits, layout)
+        check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout)
