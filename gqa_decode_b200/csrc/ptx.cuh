@@ -39,17 +39,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: every spin in these kernels gives up after kSpinLimit probes so a
-// lost signal turns into an error code instead of a hung GPU.  Each probe is a
-// try_wait, which itself blocks for a hardware-defined slice of time, so the
-// limit corresponds to seconds, far beyond any legitimate wait.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Bounded wait: every spin in these kernels gives up after kWaitLimitNs of wall time
+// (read from the global nanosecond timer), so a lost signal turns into an error code
+// instead of a hung GPU.  Legitimate waits last microseconds.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
-  return false;
 }
 
 // ---------------------------------------------------------------- TMA
