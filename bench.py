@@ -162,8 +162,8 @@ class Workload:
             import torch.distributed as dist
 
             self.dist = dist
-            self.gather_o = torch.empty(world, hq, d, dtype=torch.float32, device=dev)
-            self.gather_l = torch.empty(world, hq, dtype=torch.float32, device=dev)
+            self.gather_o = torch.empty(world * hq, d, dtype=torch.float32, device=dev)
+            self.gather_l = torch.empty(world * hq, dtype=torch.float32, device=dev)
 
     def step(self):
         G = self.G
@@ -174,9 +174,11 @@ class Workload:
         if self.name == "seqshard" and self.world > 1:
             _, o32, lse = G.gqa_decode_attention_batched(
                 self.q, self.k, self.v, None, return_f32=True, return_lse=True)
-            self.dist.all_gather_into_tensor(self.gather_o, o32)
-            self.dist.all_gather_into_tensor(self.gather_l, lse)
-            return G.merge_partials(self.gather_o, self.gather_l, out_dtype=torch.bfloat16)
+            self.dist.all_gather_into_tensor(self.gather_o, o32[0])
+            self.dist.all_gather_into_tensor(self.gather_l, lse[0])
+            w = self.world
+            return G.merge_partials(self.gather_o.view(w, -1, 128), self.gather_l.view(w, -1),
+                                    out_dtype=torch.bfloat16)
         return G.gqa_decode_attention_batched(self.q, self.k, self.v, self.seq_lens, **self.kw)
 
 
@@ -188,7 +190,7 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self.util = []
-        self._stop = threading.Event()
+        self._halt = threading.Event()
         self.ok = False
         try:
             import pynvml
@@ -215,7 +217,7 @@ class ClockSampler(threading.Thread):
         nv = self.nv
         get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
             nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
                 ut = nv.nvmlDeviceGetUtilizationRates(self.h).gpu
@@ -231,7 +233,7 @@ class ClockSampler(threading.Thread):
             time.sleep(0.05)
 
     def stop(self):
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=2)
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}

@@ -101,8 +101,10 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
   if (e != cudaSuccess) return (int)e;
   const int grows = Tr::UPPER ? 16 : 8;
   int nst = kMaxStages;
-  while (nst > 2 && decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows) > (size_t)smem_cap) --nst;
-  const size_t smem = decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows);
+  while (nst > 2 &&
+         decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows, Tr::kWarps) > (size_t)smem_cap)
+    --nst;
+  const size_t smem = decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows, Tr::kWarps);
   if (smem > (size_t)smem_cap) return GQA_ERR_SHAPE;
   prm.num_stages = nst;
   static std::atomic<unsigned long long> configured{0};  // bit per device (first 64 devices)
@@ -113,12 +115,12 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
     if (e != cudaSuccess) return (int)e;
     configured.fetch_or(bit, std::memory_order_release);
   }
-  decode_kernel<Tr><<<num_ctas, kThreads, smem, stream>>>(tk, tv, prm);
+  decode_kernel<Tr><<<num_ctas, Tr::kWarps * 32 + 32, smem, stream>>>(tk, tv, prm);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (separate_merge) {
     merge_groups_kernel<typename Tr::Q, Tr::D>
-        <<<(unsigned)groups, kConsumerThreads, 0, stream>>>(prm);
+        <<<(unsigned)groups, kMergeThreads, 0, stream>>>(prm);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }

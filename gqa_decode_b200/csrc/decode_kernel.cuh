@@ -1,13 +1,13 @@
 // Persistent split-K decode-attention kernel for sm_100a.
 //
-// One CTA per SM.  Warp 4 is the producer: one elected lane walks the CTA's share of
+// One CTA per SM.  The last warp is the producer: one elected lane walks the CTA's share of
 // the batch (schedule.cuh) and streams K and V tiles into a multi-stage shared-memory
 // ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers).
-// Warps 0-3 are consumers: each owns a quarter of every tile's keys, computes
+// The other warps (4 or 8) are consumers: each owns an equal slice of every tile's keys, computes
 // S = Q K^T for the whole query group of the KV head with mma.sync (query heads
 // padded to the 16-row MMA tile), keeps an online softmax in registers and
-// accumulates O += P V, again on the tensor cores.  At the end of a segment the four
-// warps combine their states through shared memory and write either the final output
+// accumulates O += P V, again on the tensor cores.  At the end of a segment the
+// consumer warps combine their states through shared memory and write either the final output
 // (the segment covered the whole (sequence, KV head) group) or one partial
 // (normalised O in fp32 + log-sum-exp) into the workspace; the CTA that completes a
 // group's last partial merges them (atomic ticket), so one launch does everything.
@@ -22,9 +22,8 @@
 
 namespace gqa {
 
-constexpr int kConsumerWarps = 4;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxConsumerWarps = 8;
+constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kernel
 constexpr int kMaxStages = 8;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -64,11 +63,11 @@ struct MergeSmem {
 };
 
 __host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_stages, int head_dim,
-                                                    int group_rows) {
+                                                    int group_rows, int consumer_warps) {
   size_t b = 1024;  // alignment slack
   b += (size_t)stage_bytes * num_stages;
-  b += (size_t)kConsumerWarps * group_rows * (head_dim + 8) * sizeof(float);
-  b += (size_t)kConsumerWarps * 16 * 2 * sizeof(float);
+  b += (size_t)consumer_warps * group_rows * (head_dim + 8) * sizeof(float);
+  b += (size_t)consumer_warps * 16 * 2 * sizeof(float);
   b += 2 * kMaxStages * sizeof(uint64_t);
   b += 64;
   return b;
@@ -206,12 +205,13 @@ __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_bas
   }
 }
 
-template <typename T16_, int D_, int TILE_, bool UPPER_>
+template <typename T16_, int D_, int TILE_, bool UPPER_, int WARPS_ = 4>
 struct Kv16Traits {
   using Q = T16_;
   static constexpr int D = D_;
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
+  static constexpr int kWarps = WARPS_;  // consumer warps
   static constexpr bool kFp8 = false;
   static constexpr int kBoxesPerTensor = D * 2 / 128;          // TMA boxes per K (or V) tile
   static constexpr int kBoxBytes = TILE * 128;
@@ -262,10 +262,10 @@ __device__ __forceinline__ void store_final(const DecodeParams& prm, long long o
 
 template <typename Q, int D>
 __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_slot, int n,
-                                            long long out_row0, int tid) {
+                                            long long out_row0, int tid, int nthreads) {
   const int G = prm.group;
   constexpr int D4 = D / 4;
-  for (int idx = tid; idx < G * D4; idx += kConsumerThreads) {
+  for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
     float mx = -INFINITY;
     for (int p = 0; p < n; ++p)
@@ -299,13 +299,15 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
 // The kernel.
 // ---------------------------------------------------------------------------
 template <class Tr>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Tr::kWarps * 32 + 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const DecodeParams prm) {
   using Q = typename Tr::Q;
   constexpr int D = Tr::D;
   constexpr int TILE = Tr::TILE;
   constexpr bool UPPER = Tr::UPPER;
+  constexpr int kConsumerWarps = Tr::kWarps;
+  constexpr int kConsumerThreads = kConsumerWarps * 32;
   constexpr int kRowsPerWarp = TILE / kConsumerWarps;
   static_assert(kRowsPerWarp % 16 == 0, "each consumer warp works in 16-key blocks");
   constexpr int kMoStride = MergeSmem<D>::kStride;
@@ -526,7 +528,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       bar_sync(1, kConsumerThreads);
       if (*sm_flag) {
         __threadfence();
-        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid);
+        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid, kConsumerThreads);
       }
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
@@ -537,13 +539,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 // Second-kernel merge (one CTA of 128 threads per (sequence, KV head) group), used when
 // the in-kernel merge is switched off.
 template <typename Q, int D>
-__global__ void __launch_bounds__(kConsumerThreads)
+__global__ void __launch_bounds__(kMergeThreads)
 merge_groups_kernel(const DecodeParams prm) {
   const long long g = blockIdx.x;
   const int2 info = prm.group_info[g];
   if (info.y <= 1) return;  // written directly by the decode kernel
   const long long b = g / prm.sched.num_kv_heads, h = g % prm.sched.num_kv_heads;
-  merge_group<Q, D>(prm, info.x, info.y, b * prm.num_q_heads + h * prm.group, threadIdx.x);
+  merge_group<Q, D>(prm, info.x, info.y, b * prm.num_q_heads + h * prm.group, threadIdx.x,
+                    kMergeThreads);
 }
 
 }  // namespace gqa

@@ -99,12 +99,14 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
   }
 }
 
-template <typename T16_, int TILE_, bool UPPER_>
+template <typename T16_, int TILE_, bool UPPER_, int WARPS_ = 8>
 struct KvFp8Traits {
   using Q = T16_;
   static constexpr int D = 128;
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
+  static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition hide the
+                                         // latency of the conversion chains
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
   static constexpr int kBoxBytes = TILE * 128;

@@ -1,0 +1,110 @@
+"""Multi-GPU decode: one process per GPU, ``torch.distributed`` (NCCL over NVLink) for the
+only exchange the path has.
+
+* KV-head sharding: a KV head and its query group never interact with another head
+  (gqa_decode/gqa_decode.py:58-65 of the reference: each query head attends over its own KV
+  head), so rank r simply runs the single-GPU kernels on its heads.  No collective.
+* Sequence sharding: rank r holds a contiguous slice of the keys of every head, produces
+  a normalised fp32 output and a log-sum-exp per query head, the ranks all-gather those
+  (Hq * (D + 1) floats each) and every rank merges them with the LSE-weighted merge
+  kernel - the same algebra as the reference's split-K reduction
+  (gqa_decode/gqa_decode.py:661-669), one level up.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous, balanced [begin, end) of `total` items for `rank` (first ranks get the
+    remainder)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    base, extra = divmod(total, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def shard_kv_heads(num_q_heads: int, num_kv_heads: int, world: int, rank: int):
+    """Slices of (query heads, KV heads) owned by `rank`; KV heads must divide evenly so
+    every rank keeps whole query groups."""
+    if num_kv_heads % world:
+        raise ValueError("num_kv_heads must be divisible by the number of ranks")
+    g = num_q_heads // num_kv_heads
+    per = num_kv_heads // world
+    return slice(rank * per * g, (rank + 1) * per * g), slice(rank * per, (rank + 1) * per)
+
+
+def _native_local(q, k, v, seq_lens, **kw):
+    from .gqa_decode import gqa_decode_attention_batched
+
+    _, o32, lse = gqa_decode_attention_batched(q, k, v, seq_lens, return_f32=True, return_lse=True, **kw)
+    return o32, lse
+
+
+def _native_merge(o_parts, lse_parts, out_dtype):
+    from .gqa_decode import merge_partials
+
+    return merge_partials(o_parts, lse_parts, out_dtype=out_dtype)
+
+
+def sequence_sharded_decode(
+    q: torch.Tensor,
+    k_shard: torch.Tensor,
+    v_shard: torch.Tensor,
+    seq_lens_shard: Optional[torch.Tensor] = None,
+    *,
+    group: Optional[dist.ProcessGroup] = None,
+    local_fn: Callable = _native_local,
+    merge_fn: Callable = _native_merge,
+    **kw,
+) -> torch.Tensor:
+    """Decode step when every rank holds a contiguous slice of each sequence's keys.
+
+    q ``[B, Hq, D]`` (identical on all ranks); k_shard/v_shard ``[B, Hkv, S_r, D]`` (this
+    rank's keys; ``seq_lens_shard`` gives how many of them are valid, 0 allowed).
+    Returns the full output ``[B, Hq, D]`` on every rank.  ``local_fn`` / ``merge_fn``
+    exist so the plumbing can be exercised on CPU ranks (gloo) in tests; the defaults are
+    the CUDA kernels.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    o32, lse = local_fn(q, k_shard, v_shard, seq_lens_shard, **kw)
+    b, hq, d = o32.shape
+    if world == 1:
+        return merge_fn(o32.reshape(1, b * hq, d), lse.reshape(1, b * hq), q.dtype).view(b, hq, d)
+    # one message per rank: [B*Hq, D+1] = normalised output with its log-sum-exp appended
+    mine = torch.cat([o32.reshape(b * hq, d), lse.reshape(b * hq, 1)], dim=1).contiguous()
+    flat = torch.empty((world * b * hq, d + 1), dtype=mine.dtype, device=mine.device)
+    dist.all_gather_into_tensor(flat, mine, group=group)  # rank-major concatenation
+    gathered = flat.view(world, b * hq, d + 1)
+    out = merge_fn(gathered[:, :, :d].contiguous(), gathered[:, :, d].contiguous(), q.dtype)
+    return out.view(b, hq, d)
+
+
+def head_sharded_decode(
+    q_local: torch.Tensor,
+    k_local: torch.Tensor,
+    v_local: torch.Tensor,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    gather_output: bool = False,
+    group: Optional[dist.ProcessGroup] = None,
+    local_fn: Optional[Callable] = None,
+    **kw,
+) -> torch.Tensor:
+    """Decode step when rank r owns KV heads (and their query groups) ``shard_kv_heads``.
+    The path needs no exchange; ``gather_output=True`` all-gathers the head-sharded
+    outputs into ``[B, Hq, D]`` for callers that want the whole tensor."""
+    if local_fn is None:
+        from .gqa_decode import gqa_decode_attention_batched as local_fn
+    out = local_fn(q_local, k_local, v_local, seq_lens, **kw)
+    if not gather_output or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return out
+    world = dist.get_world_size(group)
+    flat = torch.empty((world * out.shape[0],) + tuple(out.shape[1:]), dtype=out.dtype, device=out.device)
+    dist.all_gather_into_tensor(flat, out.contiguous(), group=group)  # rank-major concatenation
+    parts = flat.view((world,) + tuple(out.shape))
+    return parts.permute(1, 0, 2, 3).reshape(out.shape[0], world * out.shape[1], out.shape[2])
