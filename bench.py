@@ -42,7 +42,7 @@ import torch  # noqa: E402
 
 # dram bytes moved per algorithmic byte, from the ncu capture summarised in
 # profiles/decode_kernel_bf16_ragged.md (None until measured)
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": None, "e4m3": None}
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": 1.015, "e4m3": None}
 FALLBACK_HBM_GBS = 6650.0
 
 
