@@ -15,6 +15,7 @@ DTYPE_BF16, DTYPE_FP16, DTYPE_E4M3 = 0, 1, 2
 LAYOUT_PADDED, LAYOUT_PACKED = 0, 1
 FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
+STATIC_SCRATCH_BYTES = 8 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {
     -1: "bad argument (null/misaligned pointer or non-positive size)",
@@ -54,6 +55,7 @@ SIGNATURES = {
     "gqa_decode_attention": (ctypes.c_int, [POINTER(DecodeArgs)]),
     "gqa_decode_attention_persistent": (ctypes.c_int, [POINTER(DecodeArgs)]),
     "gqa_decode_attention_fp8": (ctypes.c_int, [POINTER(DecodeArgs)]),
+    "gqa_decode_attention_static_scratch": (ctypes.c_int, [POINTER(DecodeArgs)]),
     "gqa_merge_partials": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p,

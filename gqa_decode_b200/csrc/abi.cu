@@ -373,6 +373,46 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args) {
 
 int gqa_decode_attention_fp8(const gqa_decode_args_t* args) { return run_decode(args, true, false); }
 
+// ---- entry for callers that cannot allocate: scratch inside the library image ----------
+// The array's name is only a host-side handle in host code; kernels must be given the
+// device address that cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) unsigned char g_static_scratch[GQA_STATIC_SCRATCH_BYTES];
+static constexpr int kMaxScratchDevices = 64;
+static std::atomic<void*> g_static_scratch_addr[kMaxScratchDevices];
+
+int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args) {
+  if (!args) return GQA_ERR_ARG;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxScratchDevices) return GQA_ERR_LIMIT;
+  void* base = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!base) {
+    // set-up, once per device, with that device current
+    e = cudaGetSymbolAddress(&base, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!base) return GQA_ERR_DRIVER;
+    g_static_scratch_addr[dev].store(base, std::memory_order_release);
+  }
+  if (args->batch <= 0 || args->num_q_heads <= 0 || args->num_kv_heads <= 0 ||
+      args->num_splits < 0 || args->num_ctas < 0 || args->num_q_heads % args->num_kv_heads)
+    return GQA_ERR_ARG;
+  const int ctas = args->num_ctas > 0 ? args->num_ctas : sm_count_or(0);
+  if (ctas <= 0) return (int)cudaErrorNoDevice;
+  const long long groups = (long long)args->batch * args->num_kv_heads;
+  const WorkspaceLayout w =
+      layout_workspace(groups, max_slots(args->batch, args->num_kv_heads, ctas, args->num_splits),
+                       args->num_q_heads / args->num_kv_heads, args->head_dim);
+  if (w.total > (size_t)GQA_STATIC_SCRATCH_BYTES) return GQA_ERR_LIMIT;
+  // The array still holds the previous call's bytes: tickets and status must start at zero.
+  e = cudaMemsetAsync(base, 0, w.lse_off, static_cast<cudaStream_t>(args->stream));
+  if (e != cudaSuccess) return (int)e;
+  gqa_decode_args_t a = *args;
+  a.workspace = base;
+  a.workspace_bytes = GQA_STATIC_SCRATCH_BYTES;
+  return run_decode(&a, false, false);
+}
+
 int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num_parts,
                        int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
                        float* out_f32, float* out_lse, void* stream) {

@@ -111,6 +111,41 @@ int gqa_decode_attention(const gqa_decode_args_t* args);
  * (PersistentDecodeKernel :771). */
 int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
 
+/*
+ * Variant of gqa_decode_attention for callers that cannot hand the library a scratch
+ * buffer.  (No counterpart in the reference: its host code allocates three partial
+ * tensors per call with torch.)
+ *
+ * Who needs it: a serving engine that gave all of HBM to its own KV-cache pool at
+ * start-up, so a later cudaMalloc would fail or fragment it; a latency-critical decode
+ * loop that cannot accept the device-wide synchronisation an allocation may trigger;
+ * a host-language binding (cgo, JNI, a plugin sandbox) that can pass the tensors it was
+ * given but has no way to own and free a device buffer of its own.
+ *
+ * What it does: identical inputs, outputs and arithmetic to gqa_decode_attention
+ * (bf16/fp16 K and V, any schedule), but the partials, tickets and status word live in a
+ * fixed array of GQA_STATIC_SCRATCH_BYTES that is part of the library image; every GPU
+ * that loads the library keeps that much memory until the process exits.  args->workspace
+ * and args->workspace_bytes are ignored.  The call performs no cudaMalloc, cudaFree or
+ * any other allocation.
+ *
+ * Limits and rules:
+ *  - if the launch needs more scratch than GQA_STATIC_SCRATCH_BYTES (see
+ *    gqa_decode_workspace_bytes; roughly (batch*Hkv + #SMs) * G * (D+1) * 4 bytes for the
+ *    balanced schedule) the call returns GQA_ERR_LIMIT and launches nothing;
+ *  - the first call on each device looks up the array's device address (once per
+ *    device, with that device current); make that first call during set-up, before any
+ *    stream capture is begun;
+ *  - all calls on a device share the one array, which keeps whatever the previous call
+ *    left: the entry clears the tickets and the status word on the stream before each
+ *    launch, and two calls that overlap on the GPU (different streams, or different
+ *    host threads) race on it - serialise them;
+ *  - gqa_decode_read_status cannot be pointed at the array; a caller that wants the
+ *    status word uses the workspace-taking entry instead.
+ */
+#define GQA_STATIC_SCRATCH_BYTES (8u << 20)
+int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args);
+
 /* E4M3 K and V with per-(sequence, KV head) fp32 scales.  Replaces
  * gqa_decode_attention_fp8, gqa_decode/gqa_decode.py:1900-2010
  * (FP8DirectDecodeKernel :1454, FP8SplitKDecodeKernel :1599). */
