@@ -7,6 +7,8 @@ from .gqa_decode import (
     gqa_decode_attention_fp8,
     gqa_decode_attention_persistent,
     merge_partials,
+    plan_decode,
+    DecodePlan,
     read_status,
     reduce_partials,
     reference_gqa_decode,
@@ -21,6 +23,8 @@ __all__ = [
     "gqa_decode_attention_fp8",
     "gqa_decode_attention_persistent",
     "merge_partials",
+    "plan_decode",
+    "DecodePlan",
     "read_status",
     "reduce_partials",
     "reference_gqa_decode",

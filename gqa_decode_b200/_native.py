@@ -15,6 +15,7 @@ DTYPE_BF16, DTYPE_FP16, DTYPE_E4M3 = 0, 1, 2
 LAYOUT_PADDED, LAYOUT_PACKED = 0, 1
 FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
+FLAG_FP8_EXACT_V = 4
 STATIC_SCRATCH_BYTES = 8 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {

@@ -115,7 +115,7 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
     if (e != cudaSuccess) return (int)e;
     configured.fetch_or(bit, std::memory_order_release);
   }
-  decode_kernel<Tr><<<num_ctas, Tr::kWarps * 32 + 32, smem, stream>>>(tk, tv, prm);
+  decode_kernel<Tr><<<num_ctas, BlockShape<Tr>::kThreads, smem, stream>>>(tk, tv, prm);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (separate_merge) {
@@ -206,12 +206,21 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
 #define GQA_LAUNCH(...) \
   return launch_decode<__VA_ARGS__>(tk, tv, prm, num_ctas, st, separate, groups)
   if (fp8) {
-    if (bf) {
-      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true>);
-      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false>);
+    const bool exact_v = (a->flags & GQA_FLAG_FP8_EXACT_V) != 0;
+    if (exact_v) {
+      if (bf) {
+        if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true, true>);
+        GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false, true>);
+      }
+      if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true, true>);
+      GQA_LAUNCH(KvFp8Traits<__half, 128, false, true>);
     }
-    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true>);
-    GQA_LAUNCH(KvFp8Traits<__half, 128, false>);
+    if (bf) {
+      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true, false>);
+      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false, false>);
+    }
+    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true, false>);
+    GQA_LAUNCH(KvFp8Traits<__half, 128, false, false>);
   }
   if (D == 128) {
     if (bf) {

@@ -93,7 +93,7 @@ struct WarpState {
 
 // Online softmax over a 16-key block held as two S fragments; returns P packed for
 // the PV MMA (a0..a3) and rescales O when the running maximum moved.
-template <typename T16, int D, bool UPPER, bool PARTIAL>
+template <typename TP, int D, bool UPPER, bool PARTIAL>
 __device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPPER>& st,
                                               uint32_t (&pa)[4], float scale_log2, int key0,
                                               int valid, int lane) {
@@ -140,10 +140,10 @@ __device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPP
       }
     }
   }
-  pa[0] = Mma16<T16>::pack(p[0][0], p[0][1]);
-  pa[2] = Mma16<T16>::pack(p[1][0], p[1][1]);
-  pa[1] = UPPER ? Mma16<T16>::pack(p[0][2], p[0][3]) : 0u;
-  pa[3] = UPPER ? Mma16<T16>::pack(p[1][2], p[1][3]) : 0u;
+  pa[0] = Mma16<TP>::pack(p[0][0], p[0][1]);
+  pa[2] = Mma16<TP>::pack(p[1][0], p[1][1]);
+  pa[1] = UPPER ? Mma16<TP>::pack(p[0][2], p[0][3]) : 0u;
+  pa[3] = UPPER ? Mma16<TP>::pack(p[1][2], p[1][3]) : 0u;
 }
 
 // ---------------------------------------------------------------------------
@@ -219,6 +219,7 @@ struct Kv16Traits {
   static constexpr int kBoxCols = 64;                          // elements per box row
   struct Extra {};
   __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, const Segment&) {}
+  __device__ static __forceinline__ float out_scale(const Extra&) { return 1.f; }
   template <bool PARTIAL>
   __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
                                                  int valid, const uint32_t (&qa)[D / 16][4],
@@ -298,8 +299,19 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
 // ---------------------------------------------------------------------------
 // The kernel.
 // ---------------------------------------------------------------------------
+// Producer warps per CTA.  With 8 consumer warps the producer gets a whole warpgroup of
+// its own (only one lane works) so that `setmaxnreg` can move registers from it to the
+// two consumer warpgroups: 12 warps x 168 registers at launch become 40 for the producer
+// warpgroup and 232 for the consumers.
 template <class Tr>
-__global__ void __launch_bounds__(Tr::kWarps * 32 + 32, 1)
+struct BlockShape {
+  static constexpr int kProducerWarps = Tr::kWarps == 8 ? 4 : 1;
+  static constexpr int kThreads = (Tr::kWarps + kProducerWarps) * 32;
+  static constexpr bool kRebalanceRegs = Tr::kWarps == 8;
+};
+
+template <class Tr>
+__global__ void __launch_bounds__(BlockShape<Tr>::kThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const DecodeParams prm) {
   using Q = typename Tr::Q;
@@ -345,9 +357,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   wk.init_warp(prm.sched, blockIdx.x);
   Segment seg;
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
     // ------------------------------------------------------------ producer
-    if (lane != 0) return;
+    if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp != kConsumerWarps || lane != 0) return;
     const uint64_t policy = l2_evict_first_policy();
     uint32_t it = 0;
     bool dead = false;
@@ -378,6 +391,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
 
   // -------------------------------------------------------------- consumers
+  if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
 
@@ -463,7 +477,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w)
         L += sm_ml[(w * 16 + row) * 2 + 1] * fast_exp2(sm_ml[(w * 16 + row) * 2] - Ms);
-      const float f = L > 0.f ? fast_exp2(st.m[r] - Ms) / L : 0.f;
+      const float f = L > 0.f ? fast_exp2(st.m[r] - Ms) / L * Tr::out_scale(extra) : 0.f;
       if (row < G) {
         float* dst = sm_o + ((size_t)warp * grows + row) * kMoStride;
 #pragma unroll

@@ -2,11 +2,13 @@
 //
 // K and V tiles arrive as raw bytes ([TILE rows x 128 B], 128-byte swizzle).  Each
 // thread pulls the bytes its MMA fragments need with plain shared loads and
-// dequantises them in registers exactly as the reference's oracle does
+// dequantises them in registers.  K always follows the reference's oracle exactly
 // (gqa_decode/fp8_utils.py:54-55): float32(code) * scale[head] rounded to nearest in
 // fp32, then rounded to nearest-even to the 16-bit MMA type.  The K scale is NOT
 // folded into the score: the oracle's bf16 rounding of each dequantised element is
 // part of the answer, and dropping it moves peaked softmax rows outside tolerance.
+// V follows the same rule when EXACT_V is set; by default its scale is applied once to
+// the accumulated output instead (see consume_block_fp8).
 // Replaces FP8DirectDecodeKernel / FP8SplitKDecodeKernel
 // (gqa_decode/gqa_decode.py:1454-1596, :1599-1803; dequant at :1565-1566, :1752-1753).
 //
@@ -16,6 +18,8 @@
 // consecutive bytes of a V row feed four MMA tiles.  Q fragments and the epilogue
 // use the same permutations.
 #pragma once
+#include <type_traits>
+
 #include "decode_kernel.cuh"
 
 namespace gqa {
@@ -45,19 +49,43 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t two_codes, float scale
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)two_codes));
   const float f0 = __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
   const float f1 = __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
-  return Mma16<T16>::pack(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
+  // one packed fp32x2 multiply (round-to-nearest per lane, same result as two fmul.rn)
+  unsigned long long in, sc, prod;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(in) : "f"(f0), "f"(f1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(sc) : "f"(scale));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(in), "l"(sc));
+  float p0, p1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(prod));
+  return Mma16<T16>::pack(p0, p1);
 }
 
-template <typename T16, int TILE, bool UPPER, bool PARTIAL>
+__device__ __forceinline__ uint32_t codes_to_f16x2(uint32_t two_codes) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)two_codes));
+  return h2;
+}
+
+// EXACT_V = true : V is dequantised like K (oracle rounding) and P V runs in the query type.
+// EXACT_V = false: V codes are widened to f16 (exact) and P V runs as an f16 MMA on the
+//   unscaled codes; the per-head V scale multiplies the fp32 output once at the end.  This
+//   skips the oracle's bf16 rounding of each dequantised V element (a relative 2^-9
+//   perturbation averaged over the softmax weights, well inside the tolerance) and
+//   removes three quarters of the conversion work.
+template <typename T16, int TILE, bool UPPER, bool PARTIAL, bool EXACT_V>
 __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_base, int key0,
                                                   int valid, const uint32_t (&qa)[8][4],
                                                   WarpState<128, UPPER>& st, float scale_log2,
                                                   int lane, float k_scale, float v_scale) {
   constexpr int D = 128;
+  using TP = typename std::conditional<EXACT_V, T16, __half>::type;  // type of P and of the PV MMA
   const int n = lane >> 2, c = lane & 3;
-  float s[2][4];
+  // two accumulator sets per key tile (even / odd k-steps) halve the dependent MMA chains
+  float s[2][4], s2[2][4];
 #pragma unroll
-  for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  for (int j = 0; j < 2; ++j) {
+    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+  }
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int key = key0 + 8 * j + n;
@@ -70,12 +98,17 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
         const int ks = 4 * i + t;
         const uint32_t b0 = dequant_pair<T16>(ww[t] & 0xffffu, k_scale);
         const uint32_t b1 = dequant_pair<T16>(ww[t] >> 16, k_scale);
-        Mma16<T16>::run(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        if (t & 1) Mma16<T16>::run(s2[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        else Mma16<T16>::run(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
       }
     }
   }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
   uint32_t pa[4];
-  softmax_block<T16, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
+  softmax_block<TP, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     uint32_t w[4];
@@ -92,14 +125,20 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
     const uint32_t hi[4] = {p23a & 0xffffu, p23a >> 16, p23b & 0xffffu, p23b >> 16};
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const uint32_t b0 = dequant_pair<T16>(lo[u], v_scale);
-      const uint32_t b1 = dequant_pair<T16>(hi[u], v_scale);
-      Mma16<T16>::run(st.o[4 * q + u], pa[0], pa[1], pa[2], pa[3], b0, b1);
+      uint32_t b0, b1;
+      if (EXACT_V) {
+        b0 = dequant_pair<T16>(lo[u], v_scale);
+        b1 = dequant_pair<T16>(hi[u], v_scale);
+      } else {
+        b0 = codes_to_f16x2(lo[u]);
+        b1 = codes_to_f16x2(hi[u]);
+      }
+      Mma16<TP>::run(st.o[4 * q + u], pa[0], pa[1], pa[2], pa[3], b0, b1);
     }
   }
 }
 
-template <typename T16_, int TILE_, bool UPPER_, int WARPS_ = 8>
+template <typename T16_, int TILE_, bool UPPER_, bool EXACT_V_ = false, int WARPS_ = 8>
 struct KvFp8Traits {
   using Q = T16_;
   static constexpr int D = 128;
@@ -126,9 +165,11 @@ struct KvFp8Traits {
                                                  int valid, const uint32_t (&qa)[8][4],
                                                  WarpState<128, UPPER>& st, float scale_log2,
                                                  int lane, const Extra& e) {
-    consume_block_fp8<Q, TILE, UPPER, PARTIAL>(k_base, v_base, key0, valid, qa, st, scale_log2,
-                                               lane, e.ks, e.vs);
+    consume_block_fp8<Q, TILE, UPPER, PARTIAL, EXACT_V_>(k_base, v_base, key0, valid, qa, st,
+                                                         scale_log2, lane, e.ks, e.vs);
   }
+  // scale applied to the fp32 output when V was accumulated unscaled
+  __device__ static __forceinline__ float out_scale(const Extra& e) { return EXACT_V_ ? 1.f : e.vs; }
   // k-step ks of thread column c covers d = 32c + 16(ks/4) + 4(ks%4) + {0,1 | 2,3}.
   __device__ static __forceinline__ void load_q(uint32_t (&qa)[8][4], const Q* row0, const Q* row1,
                                                 bool v0, bool v1, int c) {

@@ -170,8 +170,10 @@ def gqa_decode_attention_batched(
     workspace: Optional[torch.Tensor] = None,
     max_seq_len: Optional[int] = None,
     num_kv_heads: Optional[int] = None,
+    fp8_exact_v: bool = False,
     _entry: str = "auto",
     _no_merge: bool = False,
+    _plan_only: bool = False,
 ):
     """One decode step for a batch of sequences with individual KV lengths.
 
@@ -185,6 +187,9 @@ def gqa_decode_attention_batched(
     ``[B, Hkv]`` (per sequence and KV head, the reference's fp8_utils scheme).
     num_splits: ``None`` = balanced persistent schedule; ``K`` = K partials per
       (sequence, KV head).
+    fp8_exact_v: round every dequantised V element to the 16-bit type as
+      ``dequantize_kv_fp8`` does (K always is); default applies the V scale to the fp32
+      output instead, which is faster and differs only in that rounding.
     Returns out ``[B, Hq, D]`` (q dtype), plus float32 output and/or natural-log LSE
     ``[B, Hq]`` when asked.  A sequence of length 0 yields zeros and LSE = -inf.
     """
@@ -273,7 +278,8 @@ def gqa_decode_attention_batched(
     a.kv_layout = code_layout
     a.num_splits, a.num_ctas = splits, num_ctas
     a.flags = (_native.FLAG_SEPARATE_MERGE if separate_merge else 0) | (
-        _native.FLAG_NO_MERGE if _no_merge else 0)
+        _native.FLAG_NO_MERGE if _no_merge else 0) | (
+        _native.FLAG_FP8_EXACT_V if fp8_exact_v else 0)
     a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     a.stream = torch.cuda.current_stream(dev).cuda_stream
@@ -283,10 +289,40 @@ def gqa_decode_attention_batched(
         fn = lib.gqa_decode_attention_persistent
     else:
         fn = lib.gqa_decode_attention
-    with torch.cuda.device(dev):
-        _native.check(fn(ctypes.byref(a)), fn.__name__ if hasattr(fn, "__name__") else "gqa_decode")
     extras = tuple(t for t in (out_f32, out_lse) if t is not None)
-    return (out, *extras) if extras else out
+    result = (out, *extras) if extras else out
+    if _plan_only:
+        keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse)
+        return DecodePlan(fn, a, dev, result, keep)
+    with torch.cuda.device(dev):
+        _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")
+    return result
+
+
+class DecodePlan:
+    """A validated, fully bound decode step: ``run()`` is one C call (two tensor-map
+    encodes and one kernel launch) on the current stream of the plan's device, with no
+    Python-side checks or allocations.  The tensors given to :func:`plan_decode` are
+    read and written in place on every run, so a serving loop updates K/V/``seq_lens``
+    storage and calls ``run()`` again.  The stream is re-read on each run."""
+
+    def __init__(self, fn, args, device, result, keep):
+        self._fn, self._args, self.device, self.result, self._keep = fn, args, device, result, keep
+        self._ref = ctypes.byref(args)
+
+    def run(self):
+        self._args.stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(self._ref)
+        if rc:
+            _native.check(rc, "gqa_decode_attention")
+        return self.result
+
+
+def plan_decode(q, k_cache, v_cache, seq_lens=None, **kw) -> DecodePlan:
+    """Validate once and return a :class:`DecodePlan` (same arguments as
+    :func:`gqa_decode_attention_batched`; the output tensors are allocated here and
+    reused by every ``run()``).  The caller must have the plan's device current."""
+    return gqa_decode_attention_batched(q, k_cache, v_cache, seq_lens, _plan_only=True, **kw)
 
 
 def _partials_for_python_reduction(q, k, v, k_scale, v_scale, splits):

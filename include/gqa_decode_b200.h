@@ -34,6 +34,9 @@ extern "C" {
 /* flags */
 #define GQA_FLAG_SEPARATE_MERGE 1 /* run the merge as a second kernel instead of in-kernel */
 #define GQA_FLAG_NO_MERGE 2       /* explicit splits only: write every partial, merge nothing */
+#define GQA_FLAG_FP8_EXACT_V 4    /* E4M3: round every dequantised V element to the 16-bit type like
+                                     dequantize_kv_fp8 (gqa_decode/fp8_utils.py:54-55) instead of
+                                     applying the V scale once to the fp32 output (default, faster) */
 
 /* errors */
 #define GQA_ERR_ARG (-1)       /* null pointer, non-positive size, misaligned pointer */

@@ -253,3 +253,50 @@ def test_sequence_shards_merge_to_whole(G):
     # and against the C-free CPU oracle on two heads' worth of data (fp64)
     exact = O.attend_one_sequence_f64(q[:8].cpu(), k[:1].cpu(), v[:1].cpu())
     assert float((whole32[0, :8].cpu().double() - exact).abs().max()) < 5e-4
+
+
+@pytest.mark.parametrize("exact_v", [False, True])
+def test_fp8_batched_exact_v_flag(G, exact_v):
+    """Both V paths (scale folded into the output / oracle-exact rounding per element) stay
+    inside the bound on outlier data, for a ragged FP8 batch with per-sequence scales."""
+    lens = [2000, 1, 4096, 129]
+    g = torch.Generator().manual_seed(77)
+    q = O.randn_bf16((len(lens), 32, 128), g)
+    smax = max(lens)
+    K8 = torch.zeros(len(lens), 8, smax, 128, dtype=torch.float8_e4m3fn)
+    V8 = torch.zeros_like(K8)
+    KS, VS, refs = [], [], []
+    for b, l in enumerate(lens):
+        k, v = O.outlier_kv((8, l, 128), g, rate=1e-2), O.outlier_kv((8, l, 128), g, rate=1e-2)
+        k8, v8, ks, vs = O.quantize_kv_e4m3(k, v)
+        K8[b, :, :l], V8[b, :, :l] = k8, v8
+        KS.append(ks), VS.append(vs)
+        refs.append(O.attend_one_sequence_e4m3(q[b], k8, v8, ks, vs))
+    out = G.gqa_decode_attention_batched(
+        q.to(DEV), K8.to(DEV), V8.to(DEV), torch.tensor(lens, dtype=torch.int32, device=DEV),
+        k_scale=torch.stack(KS).to(DEV), v_scale=torch.stack(VS).to(DEV), fp8_exact_v=exact_v)
+    _check(G, out, torch.stack(refs))
+
+
+def test_plan_and_cuda_graph_replay(G):
+    """A bound plan gives the same bits as the checked entry, also when its launch is
+    captured in a CUDA graph and replayed after the inputs changed in place."""
+    g = torch.Generator().manual_seed(8)
+    lens = [700, 3, 2049]
+    q = O.randn_bf16((3, 32, 128), g).to(DEV)
+    k = O.randn_bf16((3, 8, 2049, 128), g).to(DEV)
+    v = O.randn_bf16((3, 8, 2049, 128), g).to(DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    want = G.gqa_decode_attention_batched(q, k, v, sl).clone()
+    plan = G.plan_decode(q, k, v, sl)
+    assert torch.equal(plan.run(), want)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plan.run()
+    q.copy_(O.randn_bf16((3, 32, 128), g).to(DEV))  # new queries, same storage
+    sl.copy_(torch.tensor([1, 2049, 64], dtype=torch.int32, device=DEV))
+    want2 = G.gqa_decode_attention_batched(q, k, v, sl).clone()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(plan.result, want2)
+    assert G.read_status() == 0
