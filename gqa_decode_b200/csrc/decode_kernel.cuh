@@ -91,26 +91,28 @@ struct WarpState {
   }
 };
 
-// Online softmax over a 16-key block held as two S fragments; returns P packed for
-// the PV MMA (a0..a3) and rescales O when the running maximum moved.
-template <typename TP, int D, bool UPPER, bool PARTIAL>
-__device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPPER>& st,
-                                              uint32_t (&pa)[4], float scale_log2, int key0,
+// Online softmax over NB consecutive 16-key blocks held as 2*NB S fragments (fragment
+// t covers keys key0 + 8t .. 8t+7); returns P packed for the PV MMAs (pa[blk][0..3]) and
+// rescales O once when the running maximum moved.
+template <typename TP, int D, bool UPPER, bool PARTIAL, int NB = 1>
+__device__ __forceinline__ void softmax_block(float (&s)[2 * NB][4], WarpState<D, UPPER>& st,
+                                              uint32_t (&pa)[NB][4], float scale_log2, int key0,
                                               int valid, int lane) {
   const int c = lane & 3;
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
+  for (int t = 0; t < 2 * NB; ++t)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const bool dead = PARTIAL && (key0 + 8 * j + 2 * c + e >= valid);
-      s[j][e] = dead ? -INFINITY : s[j][e] * scale_log2;
-      if (UPPER) s[j][2 + e] = dead ? -INFINITY : s[j][2 + e] * scale_log2;
+      const bool dead = PARTIAL && (key0 + 8 * t + 2 * c + e >= valid);
+      s[t][e] = dead ? -INFINITY : s[t][e] * scale_log2;
+      if (UPPER) s[t][2 + e] = dead ? -INFINITY : s[t][2 + e] * scale_log2;
     }
   float alpha[2] = {1.f, 1.f};
-  float p[2][4];
 #pragma unroll
   for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
-    float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+    float mx = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < 2 * NB; ++t) mx = fmaxf(mx, fmaxf(s[t][2 * r], s[t][2 * r + 1]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float mnew = fmaxf(st.m[r], mx);
@@ -119,11 +121,11 @@ __device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPP
     st.m[r] = mnew;
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int t = 0; t < 2 * NB; ++t)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const float pv = fast_exp2(s[j][2 * r + e] - msafe);
-        p[j][2 * r + e] = pv;
+        const float pv = fast_exp2(s[t][2 * r + e] - msafe);
+        s[t][2 * r + e] = pv;
         sum += pv;
       }
     st.l[r] = st.l[r] * alpha[r] + sum;
@@ -140,10 +142,13 @@ __device__ __forceinline__ void softmax_block(float (&s)[2][4], WarpState<D, UPP
       }
     }
   }
-  pa[0] = Mma16<TP>::pack(p[0][0], p[0][1]);
-  pa[2] = Mma16<TP>::pack(p[1][0], p[1][1]);
-  pa[1] = UPPER ? Mma16<TP>::pack(p[0][2], p[0][3]) : 0u;
-  pa[3] = UPPER ? Mma16<TP>::pack(p[1][2], p[1][3]) : 0u;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    pa[b][0] = Mma16<TP>::pack(s[2 * b][0], s[2 * b][1]);
+    pa[b][2] = Mma16<TP>::pack(s[2 * b + 1][0], s[2 * b + 1][1]);
+    pa[b][1] = UPPER ? Mma16<TP>::pack(s[2 * b][2], s[2 * b][3]) : 0u;
+    pa[b][3] = UPPER ? Mma16<TP>::pack(s[2 * b + 1][2], s[2 * b + 1][3]) : 0u;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -178,8 +183,9 @@ __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_bas
                       r[3]);
     }
   }
-  uint32_t pa[4];
-  softmax_block<T16, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
+  uint32_t pa1[1][4];
+  softmax_block<T16, D, UPPER, PARTIAL, 1>(s, st, pa1, scale_log2, key0, valid, lane);
+  const uint32_t(&pa)[4] = pa1[0];
   // O += P V : B operand = V (k = key, n = d), transposed on load
   const int c = lane & 3;
 #pragma unroll
@@ -212,6 +218,7 @@ struct Kv16Traits {
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
   static constexpr int kWarps = WARPS_;  // consumer warps
+  static constexpr int kGroups = 1;      // consumer groups taking turns on tiles
   static constexpr bool kFp8 = false;
   static constexpr int kBoxesPerTensor = D * 2 / 128;          // TMA boxes per K (or V) tile
   static constexpr int kBoxBytes = TILE * 128;
@@ -220,13 +227,17 @@ struct Kv16Traits {
   struct Extra {};
   __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, const Segment&) {}
   __device__ static __forceinline__ float out_scale(const Extra&) { return 1.f; }
-  template <bool PARTIAL>
+  // Process the NB 16-key blocks starting at key0 of the tile.
+  template <bool PARTIAL, int NB>
   __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
                                                  int valid, const uint32_t (&qa)[D / 16][4],
                                                  WarpState<D, UPPER>& st, float scale_log2,
                                                  int lane, const Extra&) {
-    consume_block_16<Q, D, TILE, UPPER, PARTIAL>(k_base, v_base, key0, valid, qa, st, scale_log2,
-                                                 lane);
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+      if (!PARTIAL || key0 + 16 * b < valid)
+        consume_block_16<Q, D, TILE, UPPER, PARTIAL>(k_base, v_base, key0 + 16 * b, valid, qa, st,
+                                                     scale_log2, lane);
   }
   // Load the A fragments of Q for k-step ks: thread holds d = 16*ks + 2c + {0,1} and +8.
   __device__ static __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const Q* row0,
@@ -261,29 +272,58 @@ __device__ __forceinline__ void store_final(const DecodeParams& prm, long long o
   if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + out_row * D + 4 * d4) = v;
 }
 
+// `lse_smem` (capacity `lse_cap` floats) stages the group's n*G log-sum-exps so that the
+// weights come from shared memory; partial outputs are fetched eight at a time so that
+// the L2 round trips overlap instead of forming one dependent chain per partial.
+// All `nthreads` threads of named barrier 1 must call it together.
 template <typename Q, int D>
 __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_slot, int n,
-                                            long long out_row0, int tid, int nthreads) {
+                                            long long out_row0, int tid, int nthreads,
+                                            float* lse_smem, int lse_cap) {
   const int G = prm.group;
   constexpr int D4 = D / 4;
+  const float* lse_g = prm.part_lse + (size_t)first_slot * G;  // [n, G], contiguous slots
+  const bool staged = n * G <= lse_cap;
+  if (staged) {
+    for (int i = tid; i < n * G; i += nthreads) lse_smem[i] = ld_cg_f32(lse_g + i);
+    bar_sync(1, nthreads);
+  }
   for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
     float mx = -INFINITY;
-    for (int p = 0; p < n; ++p)
-      mx = fmaxf(mx, ld_cg_f32(prm.part_lse + (size_t)(first_slot + p) * G + row));
+    if (staged) {
+      for (int p = 0; p < n; ++p) mx = fmaxf(mx, lse_smem[p * G + row]);
+    } else {
+      for (int p = 0; p < n; ++p) mx = fmaxf(mx, ld_cg_f32(lse_g + (size_t)p * G + row));
+    }
     const float ms = (mx == -INFINITY) ? 0.f : mx;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    for (int p = 0; p < n; ++p) {
-      const size_t slot = (size_t)(first_slot + p);
-      const float w = fast_exp2((ld_cg_f32(prm.part_lse + slot * G + row) - ms) * kLog2e);
-      const float4 o = ld_cg_f32x4(
-          reinterpret_cast<const float4*>(prm.part_o + (slot * G + row) * D) + d4);
-      acc.x += w * o.x;
-      acc.y += w * o.y;
-      acc.z += w * o.z;
-      acc.w += w * o.w;
-      wsum += w;
+    const float4* o_g = reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
+    constexpr int kBatch = 8;
+    for (int p0 = 0; p0 < n; p0 += kBatch) {
+      float4 o[kBatch];
+      float w[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int p = p0 + u;
+        if (p < n) {
+          o[u] = ld_cg_f32x4(o_g + (size_t)p * G * D4);
+          const float l = staged ? lse_smem[p * G + row] : ld_cg_f32(lse_g + (size_t)p * G + row);
+          w[u] = fast_exp2((l - ms) * kLog2e);
+        } else {
+          o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          w[u] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        acc.x += w[u] * o[u].x;
+        acc.y += w[u] * o[u].y;
+        acc.z += w[u] * o[u].z;
+        acc.w += w[u] * o[u].w;
+        wsum += w[u];
+      }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
     acc.x *= inv;
@@ -320,8 +360,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   constexpr bool UPPER = Tr::UPPER;
   constexpr int kConsumerWarps = Tr::kWarps;
   constexpr int kConsumerThreads = kConsumerWarps * 32;
-  constexpr int kRowsPerWarp = TILE / kConsumerWarps;
+  constexpr int kGroups = Tr::kGroups;
+  constexpr int kWarpsPerGroup = kConsumerWarps / kGroups;
+  constexpr int kRowsPerWarp = TILE / kWarpsPerGroup;
   static_assert(kRowsPerWarp % 16 == 0, "each consumer warp works in 16-key blocks");
+  constexpr int NB = kRowsPerWarp / 16;
   constexpr int kMoStride = MergeSmem<D>::kStride;
 
   extern __shared__ uint8_t smem_raw[];
@@ -345,7 +388,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   if (tid == 0) {
     for (int s = 0; s < nst; ++s) {
       mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, kConsumerWarps);
+      mbar_init(empty0 + 8 * s, kWarpsPerGroup);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tm_k);
@@ -428,6 +471,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int rows = seg.row_end - seg.row_begin;
     const int ntiles = (rows + TILE - 1) / TILE;
     for (int t = 0; t < ntiles; ++t, ++it) {
+      if (kGroups > 1 && (int)(it % kGroups) != warp / kWarpsPerGroup) continue;  // other group's tile
       const uint32_t s = it % nst, ph = (it / nst) & 1u;
       if (!dead && !mbar_wait(full0 + 8 * s, ph)) {
         if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
@@ -436,22 +480,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int valid = min(TILE, rows - t * TILE);
       const uint32_t kb = stage_addr0 + s * Tr::kStageBytes;
       const uint32_t vb = kb + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+      const int key0 = (warp % kWarpsPerGroup) * kRowsPerWarp;
       if (!dead) {
-#pragma unroll
-        for (int sub = 0; sub < kRowsPerWarp / 16; ++sub) {
-          const int key0 = warp * kRowsPerWarp + sub * 16;
-          if (valid == TILE) {
-            Tr::template consume<false>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
-          } else if (key0 < valid) {
-            Tr::template consume<true>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
-          }
+        if (valid == TILE) {
+          Tr::template consume<false, NB>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
+        } else if (key0 < valid) {
+          Tr::template consume<true, NB>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }
 
-    // ---- combine the four warps' states -------------------------------------
+    // ---- combine the consumer warps' states ---------------------------------
 #pragma unroll
     for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -542,7 +583,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       bar_sync(1, kConsumerThreads);
       if (*sm_flag) {
         __threadfence();
-        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid, kConsumerThreads);
+        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid, kConsumerThreads, sm_o,
+                          kConsumerWarps * grows * kMoStride);
       }
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
@@ -558,9 +600,10 @@ merge_groups_kernel(const DecodeParams prm) {
   const long long g = blockIdx.x;
   const int2 info = prm.group_info[g];
   if (info.y <= 1) return;  // written directly by the decode kernel
+  __shared__ float lse_stage[4096];
   const long long b = g / prm.sched.num_kv_heads, h = g % prm.sched.num_kv_heads;
   merge_group<Q, D>(prm, info.x, info.y, b * prm.num_q_heads + h * prm.group, threadIdx.x,
-                    kMergeThreads);
+                    kMergeThreads, lse_stage, 4096);
 }
 
 }  // namespace gqa

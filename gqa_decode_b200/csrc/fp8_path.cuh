@@ -71,7 +71,7 @@ __device__ __forceinline__ uint32_t codes_to_f16x2(uint32_t two_codes) {
 //   skips the oracle's bf16 rounding of each dequantised V element (a relative 2^-9
 //   perturbation averaged over the softmax weights, well inside the tolerance) and
 //   removes three quarters of the conversion work.
-template <typename T16, int TILE, bool UPPER, bool PARTIAL, bool EXACT_V>
+template <typename T16, int TILE, bool UPPER, bool PARTIAL, bool EXACT_V, int NB>
 __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_base, int key0,
                                                   int valid, const uint32_t (&qa)[8][4],
                                                   WarpState<128, UPPER>& st, float scale_log2,
@@ -79,61 +79,58 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
   constexpr int D = 128;
   using TP = typename std::conditional<EXACT_V, T16, __half>::type;  // type of P and of the PV MMA
   const int n = lane >> 2, c = lane & 3;
-  // two accumulator sets per key tile (even / odd k-steps) halve the dependent MMA chains
-  float s[2][4], s2[2][4];
+  // NB blocks of 16 keys are processed together: their 2*NB score tiles are independent
+  // MMA chains, which gives the scheduler conversion work to overlap with MMA latency.
+  float s[2 * NB][4];
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
-  }
+  for (int t = 0; t < 2 * NB; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int key = key0 + 8 * j + n;
+  for (int i = 0; i < 2; ++i) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int t = 0; t < 2 * NB; ++t) {
+      const int key = key0 + 8 * t + n;
       const uint4 w = lds128(k_base + key * 128 + (((2 * c + i) ^ (key & 7)) << 4));
       const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int ks = 4 * i + t;
-        const uint32_t b0 = dequant_pair<T16>(ww[t] & 0xffffu, k_scale);
-        const uint32_t b1 = dequant_pair<T16>(ww[t] >> 16, k_scale);
-        if (t & 1) Mma16<T16>::run(s2[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-        else Mma16<T16>::run(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      for (int u = 0; u < 4; ++u) {
+        const int ks = 4 * i + u;
+        const uint32_t b0 = dequant_pair<T16>(ww[u] & 0xffffu, k_scale);
+        const uint32_t b1 = dequant_pair<T16>(ww[u] >> 16, k_scale);
+        Mma16<T16>::run(s[t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < 2; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
-  uint32_t pa[4];
-  softmax_block<TP, D, UPPER, PARTIAL>(s, st, pa, scale_log2, key0, valid, lane);
+  uint32_t pa[NB][4];
+  softmax_block<TP, D, UPPER, PARTIAL, NB>(s, st, pa, scale_log2, key0, valid, lane);
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
-    uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int kk = key0 + 2 * c + (i & 1) + (i >> 1) * 8;
-      const uint32_t addr = v_base + kk * 128 + (((2 * q + (n >> 2)) ^ (kk & 7)) << 4) + 4 * (n & 3);
-      w[i] = lds32(addr);
-      if (PARTIAL && kk >= valid) w[i] = 0u;
-    }
-    const uint32_t p01a = prmt(w[0], w[1], 0x5140u), p01b = prmt(w[0], w[1], 0x7362u);
-    const uint32_t p23a = prmt(w[2], w[3], 0x5140u), p23b = prmt(w[2], w[3], 0x7362u);
-    const uint32_t lo[4] = {p01a & 0xffffu, p01a >> 16, p01b & 0xffffu, p01b >> 16};
-    const uint32_t hi[4] = {p23a & 0xffffu, p23a >> 16, p23b & 0xffffu, p23b >> 16};
+    for (int b = 0; b < NB; ++b) {
+      uint32_t w[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      uint32_t b0, b1;
-      if (EXACT_V) {
-        b0 = dequant_pair<T16>(lo[u], v_scale);
-        b1 = dequant_pair<T16>(hi[u], v_scale);
-      } else {
-        b0 = codes_to_f16x2(lo[u]);
-        b1 = codes_to_f16x2(hi[u]);
+      for (int i = 0; i < 4; ++i) {
+        const int kk = key0 + 16 * b + 2 * c + (i & 1) + (i >> 1) * 8;
+        const uint32_t addr =
+            v_base + kk * 128 + (((2 * q + (n >> 2)) ^ (kk & 7)) << 4) + 4 * (n & 3);
+        w[i] = lds32(addr);
+        if (PARTIAL && kk >= valid) w[i] = 0u;
       }
-      Mma16<TP>::run(st.o[4 * q + u], pa[0], pa[1], pa[2], pa[3], b0, b1);
+      const uint32_t p01a = prmt(w[0], w[1], 0x5140u), p01b = prmt(w[0], w[1], 0x7362u);
+      const uint32_t p23a = prmt(w[2], w[3], 0x5140u), p23b = prmt(w[2], w[3], 0x7362u);
+      const uint32_t lo[4] = {p01a & 0xffffu, p01a >> 16, p01b & 0xffffu, p01b >> 16};
+      const uint32_t hi[4] = {p23a & 0xffffu, p23a >> 16, p23b & 0xffffu, p23b >> 16};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint32_t b0, b1;
+        if (EXACT_V) {
+          b0 = dequant_pair<T16>(lo[u], v_scale);
+          b1 = dequant_pair<T16>(hi[u], v_scale);
+        } else {
+          b0 = codes_to_f16x2(lo[u]);
+          b1 = codes_to_f16x2(hi[u]);
+        }
+        Mma16<TP>::run(st.o[4 * q + u], pa[b][0], pa[b][1], pa[b][2], pa[b][3], b0, b1);
+      }
     }
   }
 }
@@ -144,8 +141,9 @@ struct KvFp8Traits {
   static constexpr int D = 128;
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
-  static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition hide the
-                                         // latency of the conversion chains
+  static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition
+  static constexpr int kGroups = 2;      // two groups of four warps take alternate tiles, so each
+                                         // warp owns 32 keys of its tile (two independent blocks)
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
   static constexpr int kBoxBytes = TILE * 128;
@@ -160,13 +158,13 @@ struct KvFp8Traits {
     e.ks = __ldg(prm.k_scale + g);
     e.vs = __ldg(prm.v_scale + g);
   }
-  template <bool PARTIAL>
+  template <bool PARTIAL, int NB>
   __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
                                                  int valid, const uint32_t (&qa)[8][4],
                                                  WarpState<128, UPPER>& st, float scale_log2,
                                                  int lane, const Extra& e) {
-    consume_block_fp8<Q, TILE, UPPER, PARTIAL, EXACT_V_>(k_base, v_base, key0, valid, qa, st,
-                                                         scale_log2, lane, e.ks, e.vs);
+    consume_block_fp8<Q, TILE, UPPER, PARTIAL, EXACT_V_, NB>(k_base, v_base, key0, valid, qa, st,
+                                                             scale_log2, lane, e.ks, e.vs);
   }
   // scale applied to the fp32 output when V was accumulated unscaled
   __device__ static __forceinline__ float out_scale(const Extra& e) { return EXACT_V_ ? 1.f : e.vs; }
