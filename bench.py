@@ -339,8 +339,11 @@ def main():
     ap.add_argument("--workload", default="ragged",
                     choices=["ragged", "single", "fp8", "seqshard", "headshard", "headshard_fp8"])
     ap.add_argument("--batch", type=int, default=16, help="ragged workload only: sequences per rank")
-    ap.add_argument("--preheat-s", type=float, default=0.5,
-                    help="seconds of untimed steps after the warm-up (0 for profiler runs)")
+    ap.add_argument("--preheat-s", type=float, default=0.05,
+                    help="seconds of untimed steps after the warm-up so the SM clock leaves its idle "
+                         "state (0 for profiler runs).  Kept short: after about 0.3 s of continuous "
+                         "streaming the B200s of this pool settle about 8 %% below their burst "
+                         "bandwidth, and the roofline peak in MEASURED_PEAKS.json is a burst figure")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -401,7 +404,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up: W steps plus a short sustained run so clocks are at their loaded level
+    # warm-up: W steps plus a short run so the SM clock is at its loaded level
     for _ in range(max(3, args.warmup)):
         wl.step()
     torch.cuda.synchronize()
@@ -414,14 +417,16 @@ def main():
 
     # ---- device-resident timing
     barrier()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    ev[0].record()
+    # one event pair around the K steps: an event after every launch would keep launch
+    # k+1 from starting while launch k drains
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
     for i in range(args.steps):
         wl.step()
-        ev[i + 1].record()
+    ev1.record()
     barrier()
-    per_step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
-    total_ms = ev[0].elapsed_time(ev[args.steps])
+    total_ms = ev0.elapsed_time(ev1)
+    per_step_ms = [total_ms / args.steps]
     status = G.read_status()
 
     # ---- end to end from pinned host buffers

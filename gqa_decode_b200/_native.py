@@ -16,7 +16,8 @@ LAYOUT_PADDED, LAYOUT_PACKED = 0, 1
 FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
 FLAG_FP8_EXACT_V = 4
-STATIC_SCRATCH_BYTES = 8 << 20  # GQA_STATIC_SCRATCH_BYTES
+FLAG_WORK_STEALING = 8
+STATIC_SCRATCH_BYTES = 16 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {
     -1: "bad argument (null/misaligned pointer or non-positive size)",
@@ -46,6 +47,7 @@ class DecodeArgs(ctypes.Structure):
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "gqa_decode_version": (c_char_p, []),
+    "gqa_debug_set_timestamp_buffer": (ctypes.c_int, [c_void_p]),
     "gqa_decode_tile_rows": (ctypes.c_int, [c_int32, c_int32]),
     "gqa_decode_workspace_bytes": (
         ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),

@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <mutex>
 #include <cstdio>
 #include <cstring>
 
@@ -13,19 +14,40 @@
 namespace gqa {
 
 // ------------------------------------------------------------------ workspace layout
+// [status, done_ctas | chunk deques | tickets | alloc | group table | partial LSE | partial O]
 struct WorkspaceLayout {
-  size_t status_off, counters_off, info_off, lse_off, o_off, total;
+  size_t status_off, done_off, deques_off, tickets_off, alloc_off, info_off, lse_off, o_off, total;
+  long long slots;
 };
-static WorkspaceLayout layout_workspace(long long groups, long long slots, int G, int D) {
-  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+static size_t slot_bytes(int G, int D) { return (size_t)G * (D + 1) * sizeof(float); }
+static WorkspaceLayout layout_workspace(long long groups, int num_ctas, long long slots, int G,
+                                        int D) {
   WorkspaceLayout w;
   w.status_off = 0;
-  w.counters_off = 256;
-  w.info_off = up(w.counters_off + (size_t)groups * sizeof(int));
-  w.lse_off = up(w.info_off + (size_t)groups * sizeof(int2));
-  w.o_off = up(w.lse_off + (size_t)slots * G * sizeof(float));
-  w.total = up(w.o_off + (size_t)slots * G * D * sizeof(float));
+  w.done_off = 4;
+  w.deques_off = 256;
+  w.tickets_off = up256(w.deques_off + (size_t)num_ctas * sizeof(unsigned long long));
+  w.alloc_off = up256(w.tickets_off + (size_t)groups * sizeof(int));
+  w.info_off = up256(w.alloc_off + (size_t)groups * sizeof(int));
+  w.lse_off = up256(w.info_off + (size_t)groups * sizeof(int2));
+  w.o_off = up256(w.lse_off + (size_t)slots * G * sizeof(float));
+  w.total = up256(w.o_off + (size_t)slots * G * D * sizeof(float));
+  w.slots = slots;
   return w;
+}
+// Largest slot count whose layout fits in `bytes` (0 if not even the fixed part fits).
+static long long slots_that_fit(long long groups, int num_ctas, int G, int D, size_t bytes) {
+  const WorkspaceLayout w0 = layout_workspace(groups, num_ctas, 0, G, D);
+  if (bytes < w0.total + 512) return 0;
+  long long s = (long long)((bytes - w0.total - 512) / slot_bytes(G, D));
+  while (s > 0 && layout_workspace(groups, num_ctas, s, G, D).total > bytes) --s;
+  return s;
+}
+// Slots a comfortably sized workspace offers the balanced schedule: one per group plus 64
+// chunks per CTA (the chunk size adapts to whatever the caller really provides).
+static long long default_balanced_slots(long long groups, int num_ctas) {
+  return groups + 64ll * num_ctas + 1;
 }
 
 static int sm_count_or(int fallback) {
@@ -83,8 +105,15 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, int head
 }
 
 // ------------------------------------------------------------------ dispatch
+// Cost units charged per group by the balanced partition: starting and finishing a group
+// costs about 1.5 us, i.e. two 32 KB tiles of streaming or one 64 KB tile.
+static int group_overhead_for(int head_dim, int kv_dtype) {
+  return (kv_dtype == GQA_DTYPE_E4M3 || head_dim == 256) ? 1 : 2;
+}
+
 static int tile_rows_for(int head_dim, int kv_dtype) {
-  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? 128 : 0;
+  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? 256 : 0;
+  if (head_dim == 256) return 64;
   if (head_dim == 128) return 64;
   if (head_dim == 64) return 128;
   return 0;
@@ -102,9 +131,9 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
   const int grows = Tr::UPPER ? 16 : 8;
   int nst = kMaxStages;
   while (nst > 2 &&
-         decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows, Tr::kWarps) > (size_t)smem_cap)
+         decode_smem_bytes(Tr::kStageBytes, nst, Tr::kMoStride, grows, Tr::kWarps) > (size_t)smem_cap)
     --nst;
-  const size_t smem = decode_smem_bytes(Tr::kStageBytes, nst, Tr::D, grows, Tr::kWarps);
+  const size_t smem = decode_smem_bytes(Tr::kStageBytes, nst, Tr::kMoStride, grows, Tr::kWarps);
   if (smem > (size_t)smem_cap) return GQA_ERR_SHAPE;
   prm.num_stages = nst;
   static std::atomic<unsigned long long> configured{0};  // bit per device (first 64 devices)
@@ -126,6 +155,40 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
   }
   return 0;
 }
+
+// The control words at the front of a workspace (deques, tickets, counters) must be zero
+// when a launch starts.  Kernels leave them zero, but their extent depends on the batch
+// geometry, and a launch with a different geometry may find old partial data where its
+// control words live.  The library therefore remembers, per workspace pointer, the extent
+// it last left clean and clears the control region again whenever it changes (or the
+// pointer is new).
+struct WorkspaceNote {
+  const void* ptr;
+  size_t ctrl_bytes;
+};
+static std::mutex g_ws_mutex;
+static WorkspaceNote g_ws_notes[64];
+static unsigned g_ws_next = 0;
+
+static bool workspace_needs_clear(const void* ptr, size_t ctrl_bytes) {
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  for (auto& n : g_ws_notes)
+    if (n.ptr == ptr) {
+      if (n.ctrl_bytes == ctrl_bytes) return false;
+      n.ctrl_bytes = ctrl_bytes;
+      return true;
+    }
+  g_ws_notes[g_ws_next++ % 64] = WorkspaceNote{ptr, ctrl_bytes};
+  return true;
+}
+static void workspace_forget(const void* ptr) {
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  for (auto& n : g_ws_notes)
+    if (n.ptr == ptr) n = WorkspaceNote{nullptr, 0};
+}
+
+// Diagnostics: when set, every decode launch records per-CTA timestamps there.
+static std::atomic<unsigned long long*> g_timestamp_buffer{nullptr};
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -158,9 +221,29 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const int num_ctas = a->num_ctas > 0 ? a->num_ctas : sm_count_or(0);
   if (num_ctas <= 0) return (int)cudaErrorNoDevice;
   const int splits = force_balanced ? 0 : a->num_splits;
-  const long long slots = max_slots(a->batch, a->num_kv_heads, num_ctas, splits);
-  const WorkspaceLayout w = layout_workspace(groups, slots, G, D);
-  if (a->workspace_bytes < w.total) return GQA_ERR_WORKSPACE;
+  const bool no_merge = (a->flags & GQA_FLAG_NO_MERGE) != 0;
+  if (no_merge && splits == 0) return GQA_ERR_ARG;
+  const bool separate = !no_merge && (a->flags & GQA_FLAG_SEPARATE_MERGE) != 0;
+  const bool fused = !separate && !no_merge;
+  const int overhead = group_overhead_for(D, a->kv_dtype);
+  const long long tiles_per_group = ((long long)a->max_seq_len + tile - 1) / tile + overhead;
+
+  // Partial slots: explicit splits need exactly groups*K; the balanced schedule takes what
+  // the workspace offers and sizes its chunks accordingly.
+  WorkspaceLayout w;
+  int chunk = 1;
+  if (splits > 0) {
+    w = layout_workspace(groups, num_ctas, groups * splits, G, D);
+    if (a->workspace_bytes < w.total) return GQA_ERR_WORKSPACE;
+  } else {
+    long long slots = slots_that_fit(groups, num_ctas, G, D, a->workspace_bytes);
+    if (slots < groups + 2) return GQA_ERR_WORKSPACE;
+    const long long cap = default_balanced_slots(groups, num_ctas);
+    if (slots > cap) slots = cap;
+    chunk = choose_chunk_tiles(groups, tiles_per_group, num_ctas, slots);
+    if (max_slots(groups, 0, tiles_per_group, chunk) > slots) return GQA_ERR_WORKSPACE;
+    w = layout_workspace(groups, num_ctas, slots, G, D);
+  }
 
   CUtensorMap tk, tv;
   int r = make_kv_map(&tk, a->k, a->kv_dtype, D, a->total_rows, tile);
@@ -178,7 +261,10 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   prm.k_scale = a->k_scale;
   prm.v_scale = a->v_scale;
   prm.status = reinterpret_cast<int*>(ws + w.status_off);
-  prm.counters = reinterpret_cast<int*>(ws + w.counters_off);
+  prm.done_ctas = reinterpret_cast<int*>(ws + w.done_off);
+  prm.deques = reinterpret_cast<unsigned long long*>(ws + w.deques_off);
+  prm.tickets = reinterpret_cast<int*>(ws + w.tickets_off);
+  prm.alloc = reinterpret_cast<int*>(ws + w.alloc_off);
   prm.group_info = reinterpret_cast<int2*>(ws + w.info_off);
   prm.part_lse = reinterpret_cast<float*>(ws + w.lse_off);
   prm.part_o = reinterpret_cast<float*>(ws + w.o_off);
@@ -190,17 +276,24 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   prm.sched.num_ctas = num_ctas;
   prm.sched.num_splits = splits;
   prm.sched.layout = a->kv_layout;
+  prm.sched.chunk_tiles = chunk;
+  prm.sched.group_overhead = overhead;
+  // stealing needs the in-kernel merge (partials are counted as they complete)
+  prm.sched.steal = (fused && splits == 0 && (a->flags & GQA_FLAG_WORK_STEALING)) ? 1 : 0;
   prm.num_q_heads = a->num_q_heads;
   prm.group = G;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)D);
   prm.scale_log2 = scale * kLog2e;
-  const bool no_merge = (a->flags & GQA_FLAG_NO_MERGE) != 0;
-  if (no_merge && splits == 0) return GQA_ERR_ARG;
-  const bool separate = !no_merge && (a->flags & GQA_FLAG_SEPARATE_MERGE) != 0;
-  prm.fused_merge = (separate || no_merge) ? 0 : 1;
+  prm.fused_merge = fused ? 1 : 0;
   prm.no_merge = no_merge ? 1 : 0;
+  prm.num_slots = (int)w.slots;
+  prm.timestamps = g_timestamp_buffer.load(std::memory_order_relaxed);
 
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  if (workspace_needs_clear(a->workspace, w.lse_off)) {
+    cudaError_t e = cudaMemsetAsync(a->workspace, 0, w.lse_off, st);
+    if (e != cudaSuccess) return (int)e;
+  }
   const bool upper = G > 8;
   const bool bf = a->q_dtype == GQA_DTYPE_BF16;
 #define GQA_LAUNCH(...) \
@@ -209,18 +302,26 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     const bool exact_v = (a->flags & GQA_FLAG_FP8_EXACT_V) != 0;
     if (exact_v) {
       if (bf) {
-        if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true, true>);
-        GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false, true>);
+        if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, true, true>);
+        GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, false, true>);
       }
-      if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true, true>);
-      GQA_LAUNCH(KvFp8Traits<__half, 128, false, true>);
+      if (upper) GQA_LAUNCH(KvFp8Traits<__half, 256, true, true>);
+      GQA_LAUNCH(KvFp8Traits<__half, 256, false, true>);
     }
     if (bf) {
-      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, true, false>);
-      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 128, false, false>);
+      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, true, false>);
+      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, false, false>);
     }
-    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 128, true, false>);
-    GQA_LAUNCH(KvFp8Traits<__half, 128, false, false>);
+    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 256, true, false>);
+    GQA_LAUNCH(KvFp8Traits<__half, 256, false, false>);
+  }
+  if (D == 256) {
+    if (bf) {
+      if (upper) GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 256, 64, true>);
+      GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 256, 64, false>);
+    }
+    if (upper) GQA_LAUNCH(Kv16Traits<__half, 256, 64, true>);
+    GQA_LAUNCH(Kv16Traits<__half, 256, 64, false>);
   }
   if (D == 128) {
     if (bf) {
@@ -292,16 +393,47 @@ static __host__ __device__ void put_record(long long* rec, int cta, const Segmen
   rec[8] = s.kv_row0;
 }
 
+constexpr int kDumpSegs = 64;  // segments replayed per batch of walk_static calls
+
 __global__ void schedule_dump_kernel(SchedParams sp, long long* records, long long capacity,
                                      unsigned long long* count) {
   Walker wk;
-  wk.init_warp(sp, blockIdx.x);
+  wk.init_warp(sp);
+  long long t0, t1;
+  if (!wk.static_range(blockIdx.x, t0, t1)) return;
+  if (sp.num_splits > 0) wk.seek_unit_warp(t0);
+  else wk.seek_warp(t0);
   if (threadIdx.x != 0) return;
-  Segment s;
-  while (wk.next(s)) {
-    const unsigned long long i = atomicAdd(count, 1ull);
-    if ((long long)i < capacity) put_record(records + 9 * i, blockIdx.x, s);
+  // walk the CTA's static range one segment at a time
+  if (sp.num_splits > 0) {
+    for (long long u = t0; u < t1; ++u) {
+      Segment s;
+      wk.next_unit(s);
+      const unsigned long long i = atomicAdd(count, 1ull);
+      if ((long long)i < capacity) put_record(records + 9 * i, blockIdx.x, s);
+    }
+    return;
   }
+  long long t = t0;
+  while (t < t1) {
+    Segment s;
+    long long tt1 = t + (wk.ntg - wk.ti);
+    if (tt1 > t1) tt1 = t1;
+    const long long n = wk.walk_static(blockIdx.x, t, tt1, &s, 1);
+    if (n >= 1) {
+      const unsigned long long i = atomicAdd(count, 1ull);
+      if ((long long)i < capacity) put_record(records + 9 * i, blockIdx.x, s);
+    }
+    t = tt1;
+  }
+}
+
+constexpr int kDumpOverhead = 2;  // group overhead units used by the schedule dumps
+static int default_chunk(int batch, int num_kv_heads, int max_seq_len, int tile_rows, int num_ctas) {
+  const long long groups = (long long)batch * num_kv_heads;
+  return choose_chunk_tiles(groups,
+                            ((long long)max_seq_len + tile_rows - 1) / tile_rows + kDumpOverhead,
+                            num_ctas, default_balanced_slots(groups, num_ctas));
 }
 
 }  // namespace gqa
@@ -309,6 +441,12 @@ __global__ void schedule_dump_kernel(SchedParams sp, long long* records, long lo
 using namespace gqa;
 
 extern "C" {
+
+int gqa_debug_set_timestamp_buffer(uint64_t* device_buffer) {
+  g_timestamp_buffer.store(reinterpret_cast<unsigned long long*>(device_buffer),
+                           std::memory_order_relaxed);
+  return 0;
+}
 
 const char* gqa_decode_version(void) { return "gqa_decode_b200 0.1 (sm_100a)"; }
 
@@ -328,10 +466,9 @@ int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_k
   const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(1024);
   const long long groups = (long long)batch * num_kv_heads;
   // a workspace sized for the balanced schedule also has to serve explicit splits and back
-  long long slots = max_slots(batch, num_kv_heads, ctas, num_splits);
-  const long long balanced = max_slots(batch, num_kv_heads, ctas, 0);
-  if (balanced > slots) slots = balanced;
-  *bytes = layout_workspace(groups, slots, num_q_heads / num_kv_heads, head_dim).total;
+  long long slots = default_balanced_slots(groups, ctas);
+  if (groups * num_splits > slots) slots = groups * num_splits;
+  *bytes = layout_workspace(groups, ctas, slots, num_q_heads / num_kv_heads, head_dim).total + 512;
   return 0;
 }
 
@@ -339,16 +476,15 @@ int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_
                                 int32_t head_dim, int32_t num_splits, int32_t num_ctas,
                                 size_t offsets[6]) {
   if (!offsets || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
-      num_splits < 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
+      num_splits <= 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
     return GQA_ERR_ARG;
   const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(0);
   if (ctas <= 0) return (int)cudaErrorNoDevice;
+  const long long groups = (long long)batch * num_kv_heads;
   const WorkspaceLayout w =
-      layout_workspace((long long)batch * num_kv_heads,
-                       max_slots(batch, num_kv_heads, ctas, num_splits),
-                       num_q_heads / num_kv_heads, head_dim);
+      layout_workspace(groups, ctas, groups * num_splits, num_q_heads / num_kv_heads, head_dim);
   offsets[0] = w.status_off;
-  offsets[1] = w.counters_off;
+  offsets[1] = w.tickets_off;
   offsets[2] = w.info_off;
   offsets[3] = w.lse_off;
   offsets[4] = w.o_off;
@@ -362,6 +498,7 @@ int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* st
   // The counter region is bounded by the first 256-byte boundary after them, but its
   // size depends on the batch, so clear everything up to the partials conservatively:
   // tickets are only ever non-zero inside a launch, so clearing more is harmless.
+  workspace_forget(workspace);
   cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream));
   return (int)e;
 }
@@ -404,16 +541,20 @@ int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args) {
     g_static_scratch_addr[dev].store(base, std::memory_order_release);
   }
   if (args->batch <= 0 || args->num_q_heads <= 0 || args->num_kv_heads <= 0 ||
-      args->num_splits < 0 || args->num_ctas < 0 || args->num_q_heads % args->num_kv_heads)
+      args->head_dim <= 0 || args->num_splits < 0 || args->num_ctas < 0 ||
+      args->num_q_heads % args->num_kv_heads)
     return GQA_ERR_ARG;
   const int ctas = args->num_ctas > 0 ? args->num_ctas : sm_count_or(0);
   if (ctas <= 0) return (int)cudaErrorNoDevice;
   const long long groups = (long long)args->batch * args->num_kv_heads;
-  const WorkspaceLayout w =
-      layout_workspace(groups, max_slots(args->batch, args->num_kv_heads, ctas, args->num_splits),
-                       args->num_q_heads / args->num_kv_heads, args->head_dim);
-  if (w.total > (size_t)GQA_STATIC_SCRATCH_BYTES) return GQA_ERR_LIMIT;
-  // The array still holds the previous call's bytes: tickets and status must start at zero.
+  const int G = args->num_q_heads / args->num_kv_heads;
+  // Explicit splits need groups*K partial slots, the balanced schedule at least one per
+  // group (its chunk size adapts to the room there is): refuse what cannot fit the array.
+  const long long need_slots = args->num_splits > 0 ? groups * args->num_splits : groups + 2;
+  const WorkspaceLayout w = layout_workspace(groups, ctas, need_slots, G, args->head_dim);
+  if (w.total + 512 > (size_t)GQA_STATIC_SCRATCH_BYTES) return GQA_ERR_LIMIT;
+  // The array still holds the previous call's bytes: deques, tickets and status must start
+  // at zero (everything in front of the partial slots).
   e = cudaMemsetAsync(base, 0, w.lse_off, static_cast<cudaStream_t>(args->stream));
   if (e != cudaSuccess) return (int)e;
   gqa_decode_args_t a = *args;
@@ -470,17 +611,29 @@ int64_t gqa_schedule_dump(const int32_t* seq_lens_host, int32_t batch, int32_t n
   if (batch <= 0 || num_kv_heads <= 0 || max_seq_len <= 0 || tile_rows <= 0 || num_ctas <= 0 ||
       num_splits < 0 || (capacity > 0 && !records))
     return GQA_ERR_ARG;
-  SchedParams sp{seq_lens_host, batch, num_kv_heads, max_seq_len, tile_rows,
-                 num_ctas,      num_splits, kv_layout};
+  SchedParams sp{seq_lens_host, batch,      num_kv_heads, max_seq_len, tile_rows,
+                 num_ctas,      num_splits, kv_layout,
+                 default_chunk(batch, num_kv_heads, max_seq_len, tile_rows, num_ctas), kDumpOverhead, 0};
   int64_t n = 0;
   for (int c = 0; c < num_ctas; ++c) {
     Walker wk;
-    wk.init_serial(sp, c);
-    Segment s;
-    while (wk.next(s)) {
-      if (n < capacity) put_record(reinterpret_cast<long long*>(records) + 9 * n, c, s);
-      ++n;
-    }
+    wk.init_serial(sp);
+    long long t0, t1;
+    if (!wk.static_range(c, t0, t1)) continue;
+    if (num_splits > 0) wk.seek_unit_serial(t0);
+    else wk.seek_serial(t0);
+    Segment buf[kDumpSegs];
+    // segments of one CTA are produced in batches so that no large buffer is needed
+    long long got = wk.walk_static(c, t0, t1, buf, 0);  // count only
+    Walker wk2;
+    wk2.init_serial(sp);
+    if (num_splits > 0) wk2.seek_unit_serial(t0);
+    else wk2.seek_serial(t0);
+    Segment* all = got <= kDumpSegs ? buf : new Segment[got];
+    wk2.walk_static(c, t0, t1, all, got);
+    for (long long i = 0; i < got; ++i, ++n)
+      if (n < capacity) put_record(reinterpret_cast<long long*>(records) + 9 * n, c, all[i]);
+    if (all != buf) delete[] all;
   }
   return n;
 }
@@ -492,8 +645,9 @@ int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num
   if (batch <= 0 || num_kv_heads <= 0 || max_seq_len <= 0 || tile_rows <= 0 || num_ctas <= 0 ||
       num_splits < 0 || !records || !count)
     return GQA_ERR_ARG;
-  SchedParams sp{seq_lens, batch, num_kv_heads, max_seq_len, tile_rows,
-                 num_ctas, num_splits, kv_layout};
+  SchedParams sp{seq_lens, batch,      num_kv_heads, max_seq_len, tile_rows,
+                 num_ctas, num_splits, kv_layout,
+                 default_chunk(batch, num_kv_heads, max_seq_len, tile_rows, num_ctas), kDumpOverhead, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int64_t), st);
   if (e != cudaSuccess) return (int)e;

@@ -1,9 +1,11 @@
 // Persistent split-K decode-attention kernel for sm_100a.
 //
-// One CTA per SM.  The last warp is the producer: one elected lane walks the CTA's share of
-// the batch (schedule.cuh) and streams K and V tiles into a multi-stage shared-memory
+// One CTA per SM.  The producer warp is the CTA's scheduler: it takes chunks of the tile
+// line (its own range first, then chunks stolen from slower CTAs), and for every tile writes a
+// small descriptor into shared memory and streams the K and V tile into a multi-stage
 // ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers).
-// The other warps (4 or 8) are consumers: each owns an equal slice of every tile's keys, computes
+// The other warps (4 or 8) are consumers: they follow the descriptors, each owns an equal
+// slice of a tile's keys, computes
 // S = Q K^T for the whole query group of the KV head with mma.sync (query heads
 // padded to the 16-row MMA tile), keeps an online softmax in registers and
 // accumulates O += P V, again on the tensor cores.  At the end of a segment the
@@ -25,6 +27,7 @@ namespace gqa {
 constexpr int kMaxConsumerWarps = 8;
 constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kernel
 constexpr int kMaxStages = 8;
+constexpr int kDescRing = 32;  // tile descriptors kept in shared memory (>= 4 * kMaxStages)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -33,6 +36,7 @@ enum StatusBits : int {
   kStatusWaitFull = 1,    // a consumer gave up waiting for a tile
   kStatusWaitEmpty = 2,   // the producer gave up waiting for a free stage
   kStatusSmemAlign = 4,   // shared memory base not 1024-byte aligned
+  kStatusSlotRange = 8,   // a partial slot index fell outside the workspace (write skipped)
 };
 
 struct DecodeParams {
@@ -44,7 +48,10 @@ struct DecodeParams {
   const float* v_scale; // FP8 only: [batch * Hkv]
   float* part_o;        // workspace: [slots, G, D] fp32 normalised partial outputs
   float* part_lse;      // workspace: [slots, G] natural-log sum-exp per partial
-  int* counters;        // workspace: [batch * Hkv] arrival tickets, zero between launches
+  int* tickets;         // workspace: [batch * Hkv] completion tickets, zero between launches
+  int* alloc;           // workspace: [batch * Hkv] partials allocated per group, zero between launches
+  unsigned long long* deques;  // workspace: [num_ctas] chunks taken {front: low 32, back: high 32}
+  int* done_ctas;       // workspace: CTAs that finished (the last one cleans the deques)
   int* status;          // workspace: one word, OR of StatusBits
   int2* group_info;     // workspace: [batch * Hkv] {first_slot, n_parts}, written when the merge
                         // runs as a separate kernel
@@ -52,23 +59,33 @@ struct DecodeParams {
   int num_q_heads;
   int group;            // G = Hq / Hkv
   float scale_log2;     // softmax scale * log2(e)
-  int fused_merge;      // 1: last-arriving CTA merges a group's partials in this launch
+  int fused_merge;      // 1: the CTA that completes a group merges its partials in this launch
   int no_merge;         // 1: every segment is written as a partial and nothing is merged
   int num_stages;
+  int num_slots;        // partial slots the workspace holds
+  unsigned long long* timestamps;  // optional diagnostics: per CTA {start, first tile landed, end} in ns
 };
 
-template <int D>
-struct MergeSmem {
-  static constexpr int kStride = D + 8;  // floats; +8 keeps the float2 fragment stores conflict-free
+// What the producer tells the consumers about the tile in a pipeline stage.
+struct TileDesc {
+  int b, h;         // sequence and KV head
+  int valid;        // keys in this tile (0: no data was loaded - empty piece or end marker)
+  int flags;        // kTileFirst | kTileLast | kTileEnd
+  int ntg;          // tiles in the whole group
+  int first_slot;   // first partial slot of the group
+  int slot;         // slot of this segment's partial, or -1: allocate at the end of the segment
+  int n_parts;      // partials of the group if known in advance (static schedules), else 0
 };
+enum TileFlags : int { kTileFirst = 1, kTileLast = 2, kTileEnd = 4 };
 
-__host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_stages, int head_dim,
+__host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_stages, int mo_stride,
                                                     int group_rows, int consumer_warps) {
   size_t b = 1024;  // alignment slack
   b += (size_t)stage_bytes * num_stages;
-  b += (size_t)consumer_warps * group_rows * (head_dim + 8) * sizeof(float);
-  b += (size_t)consumer_warps * 16 * 2 * sizeof(float);
+  b += (size_t)consumer_warps * group_rows * mo_stride * sizeof(float);
+  b += (size_t)consumer_warps * group_rows * 2 * sizeof(float);
   b += 2 * kMaxStages * sizeof(uint64_t);
+  b += kDescRing * sizeof(TileDesc);
   b += 64;
   return b;
 }
@@ -224,8 +241,9 @@ struct Kv16Traits {
   static constexpr int kBoxBytes = TILE * 128;
   static constexpr int kStageBytes = 2 * kBoxesPerTensor * kBoxBytes;
   static constexpr int kBoxCols = 64;                          // elements per box row
+  static constexpr int kMoStride = D + 8;  // floats per merge row; +8 keeps float2 stores conflict-free
   struct Extra {};
-  __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, const Segment&) {}
+  __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, int, int) {}
   __device__ static __forceinline__ float out_scale(const Extra&) { return 1.f; }
   // Process the NB 16-key blocks starting at key0 of the tile.
   template <bool PARTIAL, int NB>
@@ -340,14 +358,163 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
 // The kernel.
 // ---------------------------------------------------------------------------
 // Producer warps per CTA.  With 8 consumer warps the producer gets a whole warpgroup of
-// its own (only one lane works) so that `setmaxnreg` can move registers from it to the
-// two consumer warpgroups: 12 warps x 168 registers at launch become 40 for the producer
-// warpgroup and 232 for the consumers.
+// its own (only one warp works) so that `setmaxnreg` can move registers from it to the
+// two consumer warpgroups: 12 warps x 168 registers at launch become 56 for the producer
+// warpgroup and 224 for the consumers.
 template <class Tr>
 struct BlockShape {
   static constexpr int kProducerWarps = Tr::kWarps == 8 ? 4 : 1;
   static constexpr int kThreads = (Tr::kWarps + kProducerWarps) * 32;
   static constexpr bool kRebalanceRegs = Tr::kWarps == 8;
+};
+
+// ------------------------------------------------------------------ producer
+template <class Tr>
+struct Producer {
+  const CUtensorMap* tm_k;
+  const CUtensorMap* tm_v;
+  const DecodeParams* prm;
+  TileDesc* sm_desc;
+  volatile int* sm_published;
+  uint32_t full0, empty0, stage_addr0;
+  uint64_t policy;
+  uint32_t it;
+  int nst, lane;
+  bool dead;
+
+  // Wait for the stage of tile `it` to be free, publish its descriptor and start the
+  // loads (or just signal when there is no data).  All lanes call it; lane 0 acts.
+  __device__ __forceinline__ void post(const TileDesc& d, long long row) {
+    if (dead) return;
+    const uint32_t s = it % nst, ph = (it / nst) & 1u;
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
+    if (!__shfl_sync(0xffffffffu, ok, 0)) {
+      if (lane == 0) atomicOr(prm->status, kStatusWaitEmpty);
+      dead = true;
+      return;
+    }
+    if (lane == 0) {
+      // The descriptor ring is much deeper than the stage ring: a consumer group that
+      // does not own this tile reads the descriptor without waiting for the tile's data.
+      sm_desc[it % kDescRing] = d;
+      __threadfence_block();
+      *sm_published = (int)(it + 1);
+      const uint32_t fb = full0 + 8 * s;
+      if (d.valid > 0) {
+        mbar_expect_tx(fb, Tr::kStageBytes);  // release: the descriptor is visible to waiters
+        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes;
+        const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+#pragma unroll
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(kdst + bx * Tr::kBoxBytes, tm_k, fb, bx * Tr::kBoxCols, (int)row, policy);
+#pragma unroll
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(vdst + bx * Tr::kBoxBytes, tm_v, fb, bx * Tr::kBoxCols, (int)row, policy);
+      } else {
+        mbar_arrive(fb);
+      }
+    }
+    __syncwarp();
+    ++it;
+  }
+};
+
+// A run of consecutive chunks [q, q + n) handed to a CTA.
+struct ChunkRun {
+  long long q;
+  int n;  // 0: nothing left anywhere
+};
+
+// Chunk hand-out.  CTA c owns the chunk range [q0, q1).  Its first part is private: the
+// owner walks it without any atomic and nobody else may touch it.  The rest is shared
+// through one 64-bit word {taken from the front by the owner : low 32 bits, taken from
+// the back by thieves : high 32 bits}; a grab is one atomicAdd and succeeds while
+// front + back stays below the shared length.  The owner takes several chunks per atomic
+// (a quarter of what is left), a thief one chunk from the CTA that has most left.
+struct ChunkSource {
+  long long q0, q1, shared0;  // own range and the start of its shared part
+  bool private_left, own_left;
+
+  __device__ __forceinline__ static long long shared_start(long long a, long long b, int steal) {
+    // without stealing everything is private; with it the last 3/8 of the range is shared
+    return steal ? b - ((b - a) * 3) / 8 : b;
+  }
+  __device__ __forceinline__ void init(const Walker& wk, int cta) {
+    wk.cta_range(cta, q0, q1);
+    shared0 = shared_start(q0, q1, wk.p.steal);
+    private_left = shared0 > q0;
+    own_left = q1 > shared0;
+  }
+  // Warp-cooperative; identical result on all lanes.
+  __device__ __forceinline__ ChunkRun next(const Walker& wk, const DecodeParams& prm, int cta,
+                                           int lane) {
+    const unsigned full = 0xffffffffu;
+    ChunkRun r{0, 0};
+    if (private_left) {
+      private_left = false;
+      r.q = q0;
+      r.n = (int)(shared0 - q0);
+      return r;
+    }
+    if (own_left) {
+      const long long ns = q1 - shared0;
+      // ask for a quarter of the shared part at a time (at least one chunk)
+      long long ask = ns / 4;
+      if (ask < 1) ask = 1;
+      unsigned long long old = 0;
+      if (lane == 0) old = atomicAdd(prm.deques + cta, (unsigned long long)ask);
+      old = __shfl_sync(full, old, 0);
+      const long long lo = (long long)(old & 0xffffffffull), hi = (long long)(old >> 32);
+      long long got = ns - hi - lo;
+      if (got > ask) got = ask;
+      if (got > 0) {
+        r.q = shared0 + lo;
+        r.n = (int)got;
+        return r;
+      }
+      own_left = false;
+    }
+    if (!wk.p.steal) return r;
+    for (int attempt = 0; attempt < 8; ++attempt) {
+      long long best = 0;
+      int victim = -1;
+      for (int v = lane; v < (int)wk.parts; v += 32) {
+        if (v == cta) continue;
+        long long a, b;
+        wk.cta_range(v, a, b);
+        const long long vs = b - shared_start(a, b, 1);
+        const unsigned long long w = __ldcg(prm.deques + v);
+        const long long left = vs - (long long)(w & 0xffffffffull) - (long long)(w >> 32);
+        if (left > best) {
+          best = left;
+          victim = v;
+        }
+      }
+      for (int o = 16; o; o >>= 1) {
+        const long long ob = __shfl_xor_sync(full, best, o);
+        const int ov = __shfl_xor_sync(full, victim, o);
+        if (ob > best || (ob == best && ov > victim)) {
+          best = ob;
+          victim = ov;
+        }
+      }
+      if (best <= 0 || victim < 0) return r;
+      long long a, b;
+      wk.cta_range(victim, a, b);
+      const long long vs = b - shared_start(a, b, 1);
+      unsigned long long old = 0;
+      if (lane == 0) old = atomicAdd(prm.deques + victim, 1ull << 32);
+      old = __shfl_sync(full, old, 0);
+      const long long lo = (long long)(old & 0xffffffffull), hi = (long long)(old >> 32);
+      if (lo + hi < vs) {
+        r.q = b - 1 - hi;
+        r.n = 1;
+        return r;
+      }
+    }
+    return r;
+  }
 };
 
 template <class Tr>
@@ -365,7 +532,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   constexpr int kRowsPerWarp = TILE / kWarpsPerGroup;
   static_assert(kRowsPerWarp % 16 == 0, "each consumer warp works in 16-key blocks");
   constexpr int NB = kRowsPerWarp / 16;
-  constexpr int kMoStride = MergeSmem<D>::kStride;
+  constexpr int kMoStride = Tr::kMoStride;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -377,134 +544,262 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint8_t* stage0 = smem;
   float* sm_o = reinterpret_cast<float*>(smem + (size_t)nst * Tr::kStageBytes);
   float* sm_ml = sm_o + (size_t)kConsumerWarps * grows * kMoStride;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm_ml + kConsumerWarps * 16 * 2);
-  int* sm_flag = reinterpret_cast<int*>(bars + 2 * kMaxStages);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm_ml + kConsumerWarps * grows * 2);
+  TileDesc* sm_desc = reinterpret_cast<TileDesc*>(bars + 2 * kMaxStages);
+  int* sm_flag = reinterpret_cast<int*>(sm_desc + kDescRing);
+  volatile int* sm_published = sm_flag + 1;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
   const uint32_t stage_addr0 = smem_u32(stage0);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  const int Hkv = prm.sched.num_kv_heads;
 
   if (tid == 0) {
     for (int s = 0; s < nst; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, kWarpsPerGroup);
     }
+    *sm_published = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
   __syncthreads();
-
-  Walker wk;
-  wk.init_warp(prm.sched, blockIdx.x);
-  Segment seg;
+  if (prm.timestamps && tid == 0) prm.timestamps[3 * blockIdx.x] = global_timer_ns();
 
   if (warp >= kConsumerWarps) {
-    // ------------------------------------------------------------ producer
-    if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp != kConsumerWarps || lane != 0) return;
-    const uint64_t policy = l2_evict_first_policy();
-    uint32_t it = 0;
-    bool dead = false;
-    while (!dead && wk.next(seg)) {
-      const int rows = seg.row_end - seg.row_begin;
-      const int ntiles = (rows + TILE - 1) / TILE;
-      for (int t = 0; t < ntiles; ++t, ++it) {
-        const uint32_t s = it % nst, ph = (it / nst) & 1u;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) {
-          atomicOr(prm.status, kStatusWaitEmpty);
-          dead = true;
-          break;
+    // ------------------------------------------------------------ producer warp
+    if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp != kConsumerWarps) return;
+    Walker wk;
+    wk.init_warp(prm.sched);
+    Producer<Tr> pr;
+    pr.tm_k = &tm_k;
+    pr.tm_v = &tm_v;
+    pr.prm = &prm;
+    pr.sm_desc = sm_desc;
+    pr.sm_published = sm_published;
+    pr.full0 = full0;
+    pr.empty0 = empty0;
+    pr.stage_addr0 = stage_addr0;
+    pr.policy = l2_evict_first_policy();
+    pr.it = 0;
+    pr.nst = nst;
+    pr.lane = lane;
+    pr.dead = false;
+    const int cta = blockIdx.x;
+    TileDesc d;
+    if (prm.sched.num_splits > 0) {
+      // explicit split-K: a static run of (group, piece) units, one segment each
+      long long u0, u1;
+      wk.cta_range(cta, u0, u1);
+      if (u1 > u0) wk.seek_unit_warp(u0);
+      for (long long u = u0; u < u1 && !pr.dead; ++u) {
+        Segment sg;
+        wk.next_unit(sg);
+        const int rows = sg.row_end - sg.row_begin;
+        const int ntiles = (rows + TILE - 1) / TILE;
+        d.b = sg.b;
+        d.h = sg.h;
+        d.ntg = ntiles;
+        d.first_slot = sg.first_slot;
+        d.slot = sg.slot;
+        d.n_parts = sg.n_parts;
+        if (ntiles == 0) {
+          d.valid = 0;
+          d.flags = kTileFirst | kTileLast;
+          pr.post(d, 0);
         }
-        const uint32_t fb = full0 + 8 * s;
-        mbar_expect_tx(fb, Tr::kStageBytes);
-        const long long row = seg.kv_row0 + seg.row_begin + (long long)t * TILE;
-        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes;
-        const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
-#pragma unroll
-        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-          tma_load_2d(kdst + bx * Tr::kBoxBytes, &tm_k, fb, bx * Tr::kBoxCols, (int)row, policy);
-#pragma unroll
-        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-          tma_load_2d(vdst + bx * Tr::kBoxBytes, &tm_v, fb, bx * Tr::kBoxCols, (int)row, policy);
+        for (int t = 0; t < ntiles; ++t) {
+          d.valid = min(TILE, rows - t * TILE);
+          d.flags = (t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0);
+          pr.post(d, sg.kv_row0 + sg.row_begin + (long long)t * TILE);
+        }
+      }
+    } else {
+      ChunkSource src;
+      src.init(wk, cta);
+      ChunkRun cur = src.next(wk, prm, cta, lane);
+      long long t = 0, t_end = 0, tmp;
+      if (cur.n > 0) {
+        wk.chunk_tile_range(cur.q, t, tmp);
+        wk.chunk_tile_range(cur.q + cur.n - 1, tmp, t_end);
+        wk.seek_warp(t);
+      }
+      bool open = false;
+      int cached_group = -1;  // group whose per-group descriptor fields are in `d`
+      long long row0 = 0;
+      while (cur.n > 0 && !pr.dead) {
+        ChunkRun nxt{0, 0};
+        bool contiguous = false;
+        for (; t < t_end; ++t) {
+          if (t == t_end - 1) {
+            // only the last tile of a run needs to know whether the segment continues:
+            // fetch the next run now (the ring is full, so the atomic's latency is hidden)
+            nxt = src.next(wk, prm, cta, lane);
+            contiguous = nxt.n > 0 && nxt.q == cur.q + cur.n;
+          }
+          if (wk.ti < 0) {  // a unit of the group's fixed overhead: nothing to load
+            wk.advance();
+            continue;
+          }
+          const int gi = wk.b * Hkv + wk.h;
+          if (gi != cached_group) {
+            // per-group values (a few 64-bit divisions) are computed once per group
+            cached_group = gi;
+            d.b = wk.b;
+            d.h = wk.h;
+            d.ntg = wk.ntg;
+            d.first_slot = wk.group_first_slot();
+            if (prm.sched.steal) {
+              d.slot = -1;
+              d.n_parts = 0;
+            } else {
+              d.slot = d.first_slot + wk.group_static_index(cta);
+              d.n_parts = wk.group_static_parts();
+            }
+            row0 = wk.kv_row0();
+          }
+          const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
+          d.valid = min(TILE, wk.len - wk.ti * TILE);
+          d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0);
+          pr.post(d, row0 + (long long)wk.ti * TILE);
+          open = !last;
+          wk.advance();
+        }
+        if (nxt.n <= 0) break;
+        wk.chunk_tile_range(nxt.q, t, tmp);
+        wk.chunk_tile_range(nxt.q + nxt.n - 1, tmp, t_end);
+        if (!contiguous) {
+          wk.seek_warp(t);
+          cached_group = -1;
+        }
+        cur = nxt;
       }
     }
+    d.valid = 0;
+    d.flags = kTileEnd;
+    pr.post(d, 0);
     return;
   }
 
   // -------------------------------------------------------------- consumers
-  if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+  if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
+  const bool dynamic = prm.sched.num_splits == 0 && prm.sched.steal;
 
-  // Sequences without keys own no tiles in balanced mode: their outputs are zeros.
+  // Sequences without keys own no tiles in the balanced schedule: their outputs are zeros.
   if (prm.sched.num_splits == 0 && prm.sched.seq_lens) {
     for (int b = blockIdx.x; b < prm.sched.batch; b += gridDim.x) {
-      if (wk.len_of(b) > 0) continue;
+      if (__ldg(prm.sched.seq_lens + b) > 0) continue;
       for (int idx = tid; idx < Hq * (D / 4); idx += kConsumerThreads) {
         const int row = idx / (D / 4), d4 = idx % (D / 4);
         store_final<Q, D>(prm, (long long)b * Hq + row, d4, make_float4(0.f, 0.f, 0.f, 0.f));
         if (d4 == 0 && prm.out_lse) prm.out_lse[(long long)b * Hq + row] = -INFINITY;
       }
       if (!prm.fused_merge)
-        for (int h = tid; h < prm.sched.num_kv_heads; h += kConsumerThreads)
-          prm.group_info[(long long)b * prm.sched.num_kv_heads + h] = make_int2(0, 1);
+        for (int h = tid; h < Hkv; h += kConsumerThreads)
+          prm.group_info[(long long)b * Hkv + h] = make_int2(0, 1);
     }
   }
 
   WarpState<D, UPPER> st;
   uint32_t qa[D / 16][4];
   typename Tr::Extra extra;
-  uint32_t it = 0;
-  bool dead = false;
+  int seg_tiles = 0;
 
-  while (wk.next(seg)) {
-    const long long out_row0 = (long long)seg.b * Hq + (long long)seg.h * G;
-    {
+  for (uint32_t it = 0;; ++it) {
+    const uint32_t s = it % nst, ph = (it / nst) & 1u;
+    // With several consumer groups a tile (and its stage barriers) belongs to one group;
+    // the other groups only need its descriptor, which they take once it is published.
+    const bool mine = kGroups == 1 || (int)(it % kGroups) == warp / kWarpsPerGroup;
+    bool ok = true;
+    if (mine) {
+      ok = mbar_wait(full0 + 8 * s, ph);
+    } else {
+      const unsigned long long t0 = global_timer_ns();
+      while (*sm_published <= (int)it) {
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+          ok = false;
+          break;
+        }
+      }
+      __threadfence_block();
+    }
+    if (!ok) {
+      // the producer stopped: every consumer warp runs into this within the same tile or two
+      if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
+      break;
+    }
+    const TileDesc d = sm_desc[it % kDescRing];
+    if (d.flags & kTileEnd) break;
+    if (prm.timestamps && tid == 0 && it == 0) prm.timestamps[3 * blockIdx.x + 1] = global_timer_ns();
+    const long long g = (long long)d.b * Hkv + d.h;
+    const long long out_row0 = (long long)d.b * Hq + (long long)d.h * G;
+    if (d.flags & kTileFirst) {
       const Q* qbase = reinterpret_cast<const Q*>(prm.q) + out_row0 * D;
       Tr::load_q(qa, qbase + (size_t)r0 * D, qbase + (size_t)(r0 + 8) * D, r0 < G,
                  UPPER && (r0 + 8 < G), c);
+      Tr::begin_segment(extra, prm, d.b, d.h);
+      st.reset();
+      seg_tiles = 0;
     }
-    Tr::begin_segment(extra, prm, seg);
-    st.reset();
-    const int rows = seg.row_end - seg.row_begin;
-    const int ntiles = (rows + TILE - 1) / TILE;
-    for (int t = 0; t < ntiles; ++t, ++it) {
-      if (kGroups > 1 && (int)(it % kGroups) != warp / kWarpsPerGroup) continue;  // other group's tile
-      const uint32_t s = it % nst, ph = (it / nst) & 1u;
-      if (!dead && !mbar_wait(full0 + 8 * s, ph)) {
-        if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
-        dead = true;
-      }
-      const int valid = min(TILE, rows - t * TILE);
-      const uint32_t kb = stage_addr0 + s * Tr::kStageBytes;
-      const uint32_t vb = kb + Tr::kBoxesPerTensor * Tr::kBoxBytes;
-      const int key0 = (warp % kWarpsPerGroup) * kRowsPerWarp;
-      if (!dead) {
-        if (valid == TILE) {
-          Tr::template consume<false, NB>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
-        } else if (key0 < valid) {
-          Tr::template consume<true, NB>(kb, vb, key0, valid, qa, st, prm.scale_log2, lane, extra);
+    if (d.valid > 0) {
+      ++seg_tiles;
+      if (mine) {
+        const uint32_t kb = stage_addr0 + s * Tr::kStageBytes;
+        const uint32_t vb = kb + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+        const int key0 = (warp % kWarpsPerGroup) * kRowsPerWarp;
+        if (d.valid == TILE) {
+          Tr::template consume<false, NB>(kb, vb, key0, d.valid, qa, st, prm.scale_log2, lane, extra);
+        } else if (key0 < d.valid) {
+          Tr::template consume<true, NB>(kb, vb, key0, d.valid, qa, st, prm.scale_log2, lane, extra);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+    __syncwarp();
+    if (mine && lane == 0) mbar_arrive(empty0 + 8 * s);
+    if (!(d.flags & kTileLast)) continue;
+
+    // The next descriptor (normally published long ago) starts a new segment: pull its
+    // query rows towards L1 now, so that their load does not wait behind this epilogue.
+    if (*sm_published > (int)(it + 1)) {
+      __threadfence_block();
+      const TileDesc nd = sm_desc[(it + 1) % kDescRing];
+      if ((nd.flags & kTileFirst) && tid < G * (D * 2 / 128)) {
+        const char* qn = reinterpret_cast<const char*>(prm.q) +
+                         ((long long)nd.b * Hq + (long long)nd.h * G) * D * 2 + (size_t)tid * 128;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(qn));
+      }
     }
 
-    // ---- combine the consumer warps' states ---------------------------------
+    // ---- end of a segment: combine the consumer warps' states ------------------------
 #pragma unroll
     for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
     }
     if (c == 0) {
-      sm_ml[(warp * 16 + r0) * 2 + 0] = st.m[0];
-      sm_ml[(warp * 16 + r0) * 2 + 1] = st.l[0];
+      sm_ml[(warp * grows + r0) * 2 + 0] = st.m[0];
+      sm_ml[(warp * grows + r0) * 2 + 1] = st.l[0];
       if (UPPER) {
-        sm_ml[(warp * 16 + r0 + 8) * 2 + 0] = st.m[1];
-        sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = st.l[1];
+        sm_ml[(warp * grows + r0 + 8) * 2 + 0] = st.m[1];
+        sm_ml[(warp * grows + r0 + 8) * 2 + 1] = st.l[1];
       }
+    }
+    // a partial needs a slot: static schedules know it, the stealing schedule takes the
+    // group's next free one (the atomic overlaps the combine below)
+    const bool direct =
+        !prm.no_merge && (dynamic ? seg_tiles == d.ntg : d.n_parts == 1);
+    if (tid == 0 && !direct) {
+      int sl = d.slot >= 0 ? d.slot : d.first_slot + atomicAdd(prm.alloc + g, 1);
+      if (sl < 0 || sl >= prm.num_slots) {  // cannot happen with clean control words; never write outside
+        atomicOr(prm.status, kStatusSlotRange);
+        sl = -1;
+      }
+      *sm_flag = sl;
     }
     bar_sync(1, kConsumerThreads);
 #pragma unroll
@@ -512,12 +807,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int row = r0 + 8 * r;
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * 16 + row) * 2]);
+      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * grows + row) * 2]);
       const float Ms = (M == -INFINITY) ? 0.f : M;
       float L = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w)
-        L += sm_ml[(w * 16 + row) * 2 + 1] * fast_exp2(sm_ml[(w * 16 + row) * 2] - Ms);
+        L += sm_ml[(w * grows + row) * 2 + 1] * fast_exp2(sm_ml[(w * grows + row) * 2] - Ms);
       const float f = L > 0.f ? fast_exp2(st.m[r] - Ms) / L * Tr::out_scale(extra) : 0.f;
       if (row < G) {
         float* dst = sm_o + ((size_t)warp * grows + row) * kMoStride;
@@ -533,8 +828,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
       }
     }
+    const int slot = direct ? 0 : *sm_flag;
     bar_sync(1, kConsumerThreads);
-    const bool direct = seg.n_parts == 1 && !prm.no_merge;
     for (int idx = tid; idx < G * (D / 4); idx += kConsumerThreads) {
       const int row = idx / (D / 4), d4 = idx % (D / 4);
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -548,47 +843,70 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         acc.w += v.w;
       }
       if (direct) store_final<Q, D>(prm, out_row0 + row, d4, acc);
-      else
-        *reinterpret_cast<float4*>(prm.part_o + ((size_t)seg.slot * G + row) * D + 4 * d4) = acc;
+      else if (slot >= 0)
+        *reinterpret_cast<float4*>(prm.part_o + ((size_t)slot * G + row) * D + 4 * d4) = acc;
     }
     if (tid < G) {
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * 16 + tid) * 2]);
+      for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sm_ml[(w * grows + tid) * 2]);
       const float Ms = (M == -INFINITY) ? 0.f : M;
       float L = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w)
-        L += sm_ml[(w * 16 + tid) * 2 + 1] * fast_exp2(sm_ml[(w * 16 + tid) * 2] - Ms);
+        L += sm_ml[(w * grows + tid) * 2 + 1] * fast_exp2(sm_ml[(w * grows + tid) * 2] - Ms);
       const float lse = L > 0.f ? (Ms + fast_log2(L)) * kLn2 : -INFINITY;
       if (direct) {
         if (prm.out_lse) prm.out_lse[out_row0 + tid] = lse;
-      } else {
-        prm.part_lse[(size_t)seg.slot * G + tid] = lse;
+      } else if (slot >= 0) {
+        prm.part_lse[(size_t)slot * G + tid] = lse;
       }
     }
-    if (!prm.fused_merge && tid == 0 && seg.slot == seg.first_slot)
-      prm.group_info[(long long)seg.b * prm.sched.num_kv_heads + seg.h] =
-          make_int2(seg.first_slot, seg.n_parts);
+    if (!prm.fused_merge && tid == 0) {
+      if (direct) prm.group_info[g] = make_int2(0, 1);
+      else if (slot == d.first_slot) prm.group_info[g] = make_int2(d.first_slot, d.n_parts);
+    }
     if (!direct && prm.fused_merge) {
+      // publish the partial, then draw a ticket: tiles covered (stealing schedule) or one
+      // per partial (static schedules); whoever completes the group merges it
       __threadfence();
       bar_sync(1, kConsumerThreads);
       if (tid == 0) {
-        int* ctr = prm.counters + ((long long)seg.b * prm.sched.num_kv_heads + seg.h);
-        const int ticket = atomicAdd(ctr, 1);
-        const int last = ticket == seg.n_parts - 1;
-        if (last) *ctr = 0;  // every contributor has arrived: leave the counter clean
-        *sm_flag = last;
+        const int add = dynamic ? seg_tiles : 1, want = dynamic ? d.ntg : d.n_parts;
+        const int before = atomicAdd(prm.tickets + g, add);
+        int n = 0;
+        if (before + add == want) {
+          __threadfence();
+          n = dynamic ? atomicAdd(prm.alloc + g, 0) : d.n_parts;
+          if (n < 0 || d.first_slot + n > prm.num_slots) {
+            atomicOr(prm.status, kStatusSlotRange);
+            n = 0;
+          }
+          prm.tickets[g] = 0;  // every contributor has arrived: leave the counters clean
+          prm.alloc[g] = 0;
+        }
+        *sm_flag = n;
       }
       bar_sync(1, kConsumerThreads);
-      if (*sm_flag) {
+      const int n = *sm_flag;
+      if (n > 0) {
         __threadfence();
-        merge_group<Q, D>(prm, seg.first_slot, seg.n_parts, out_row0, tid, kConsumerThreads, sm_o,
+        merge_group<Q, D>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads, sm_o,
                           kConsumerWarps * grows * kMoStride);
       }
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
     bar_sync(1, kConsumerThreads);
+  }
+
+  if (tid == 0) {
+    if (prm.timestamps) prm.timestamps[3 * blockIdx.x + 2] = global_timer_ns();
+    // the last CTA to finish leaves the chunk deques clean for the next launch
+    __threadfence();
+    if (atomicAdd(prm.done_ctas, 1) == (int)gridDim.x - 1) {
+      for (int i = 0; i < prm.sched.num_ctas; ++i) prm.deques[i] = 0ull;
+      *prm.done_ctas = 0;
+    }
   }
 }
 

@@ -142,8 +142,10 @@ struct KvFp8Traits {
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
   static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition
-  static constexpr int kGroups = 2;      // two groups of four warps take alternate tiles, so each
-                                         // warp owns 32 keys of its tile (two independent blocks)
+  static constexpr int kGroups = TILE_ == 128 ? 2 : 1;  // 128-key tiles: two groups of four warps
+                                         // take alternate tiles; either way a warp owns 32 keys of
+                                         // a tile (two independent 16-key blocks)
+  static constexpr int kMoStride = 128 + 4;  // floats per merge row
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
   static constexpr int kBoxBytes = TILE * 128;
@@ -152,9 +154,9 @@ struct KvFp8Traits {
   struct Extra {
     float ks, vs;
   };
-  __device__ static __forceinline__ void begin_segment(Extra& e, const DecodeParams& prm,
-                                                       const Segment& seg) {
-    const long long g = (long long)seg.b * prm.sched.num_kv_heads + seg.h;
+  __device__ static __forceinline__ void begin_segment(Extra& e, const DecodeParams& prm, int b,
+                                                       int h) {
+    const long long g = (long long)b * prm.sched.num_kv_heads + h;
     e.ks = __ldg(prm.k_scale + g);
     e.vs = __ldg(prm.v_scale + g);
   }

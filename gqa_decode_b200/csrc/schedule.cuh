@@ -1,25 +1,35 @@
 // Work scheduler shared by host and device code.
 //
 // The KV cache of a batch is cut into tiles of `tile_rows` keys.  A "group" is one
-// (sequence, KV head) pair; its tiles are consecutive.  Two policies hand tiles to
-// the persistent CTAs:
+// (sequence, KV head) pair; its tiles are consecutive.  All tiles of the batch, in
+// (sequence, KV head, tile) order, form one line.  Every group additionally contributes
+// `group_overhead` cost units in front of its tiles: starting and finishing a group
+// (query load, cross-warp combine, output write) costs about as much as streaming a
+// couple of tiles, and a partition that ignored it would hand a CTA that owns many
+// one-tile groups twice the work of its neighbours.  The line is therefore measured in
+// units; a unit is either a tile or a slice of a group's overhead.
 //
-//   balanced (num_splits == 0): all tiles of the batch, in (sequence, KV head, tile)
-//     order, are divided into `num_ctas` contiguous ranges of equal size (+-1).  A CTA
-//     therefore owns a few "segments" (maximal runs inside one group).  Ragged
-//     lengths cost nothing: a long sequence simply spans more CTAs.  This replaces the
-//     reference's PersistentDecodeKernel work loop (gqa_decode/gqa_decode.py:865,
-//     :902-907) and its host-side sizing (:1408-1410), which recompiles per length
-//     and handles one sequence only.
+//   balanced (num_splits == 0): the line is cut into M chunks of `chunk_tiles` tiles and
+//     CTA c owns the chunk range [c*M/P, (c+1)*M/P), P = min(#CTAs, M).  A CTA works
+//     through its own range from the front; consecutive chunks fuse into one running
+//     segment, so an undisturbed CTA produces one partial per group it touches, exactly
+//     like a static split.  A CTA that runs dry steals single chunks from the back of
+//     other CTAs' ranges (kernel side, decode_kernel.cuh).  SMs do not stream at the same
+//     speed - on B200 the slowest SM needs about 1.3x the time of the fastest for the same
+//     bytes - so equal static shares leave most SMs idle while the slowest finishes.
+//     Ragged lengths cost nothing: a long sequence simply spans more chunks.  This
+//     replaces the reference's PersistentDecodeKernel work loop
+//     (gqa_decode/gqa_decode.py:865, :902-907) and its host-side sizing (:1408-1410),
+//     which recompiles per length and handles one sequence.
 //
-//   explicit (num_splits == K > 0): every group is cut into K chunks of
-//     ceil(tiles/K) tiles, the classic split-K grid of the reference
-//     (gqa_decode/gqa_decode.py:273-274, :1104-1105); units (group, chunk) are dealt to
-//     CTAs in contiguous runs.
+//   explicit (num_splits == K > 0): every group is cut into K pieces of ceil(tiles/K)
+//     tiles, the classic split-K grid of the reference (gqa_decode/gqa_decode.py:273-274,
+//     :1104-1105); units (group, piece) are dealt to CTAs in contiguous static runs.
 //
-// Each segment produces one partial (normalised O, log-sum-exp) in a numbered slot.
-// In balanced mode slot = cta + group: both indices grow monotonically along the
-// tile order, so the sum is unique and a group's partials occupy consecutive slots.
+// A "segment" is a run of tiles of one group processed by one CTA without interruption;
+// it produces one partial (normalised O, log-sum-exp).  Partial slots of a group start at
+// first_slot = (chunk of the group's first tile) + group index: both terms grow along the
+// line, so groups get disjoint slot ranges with room for one partial per chunk.
 #pragma once
 #include <stdint.h>
 
@@ -40,34 +50,44 @@ struct SchedParams {
   const int32_t* seq_lens;  // [batch] KV length per sequence; null = every sequence has max_seq keys
   int batch;
   int num_kv_heads;
-  int max_seq;     // rows per head slab (padded layout) and upper bound of any length
-  int tile_rows;   // keys per pipeline stage
-  int num_ctas;    // persistent CTAs
-  int num_splits;  // 0 = balanced, K > 0 = explicit split-K
-  int layout;      // KvLayout
+  int max_seq;      // rows per head slab (padded layout) and upper bound of any length
+  int tile_rows;    // keys per pipeline stage
+  int num_ctas;     // persistent CTAs
+  int num_splits;   // 0 = balanced, K > 0 = explicit split-K
+  int layout;       // KvLayout
+  int chunk_tiles;  // balanced: units per chunk (>= 1)
+  int group_overhead;  // balanced: cost units charged per (sequence, KV head) group
+  int steal;        // balanced: 1 = idle CTAs steal chunks (results then depend on timing in
+                    // the last float32 bits), 0 = static ranges only (bit-reproducible)
 };
 
+// One run of tiles inside one group, as reported by the host-side replay of the static
+// schedule (and used by the explicit split mode on the device).
 struct Segment {
   int b, h;                // sequence and KV head
   int len;                 // keys in the sequence
   int row_begin, row_end;  // key range [row_begin, row_end) handled by this segment (may be empty)
   long long kv_row0;       // row of key 0 of this (b,h) slab in the 2-D [rows, D] view of K and V
-  int slot;                // partial slot written by this segment
+  int slot;                // partial slot written by this segment (static schedule)
   int first_slot;          // first slot of the group
-  int n_parts;             // partials the group is made of (1 = the segment is the whole group)
+  int n_parts;             // partials the group is made of in the static schedule
 };
 
 struct Walker {
   SchedParams p;
-  int cta;
-  long long total;  // balanced: tiles in the batch; explicit: units in the batch
-  long long parts;  // balanced: CTAs that actually receive tiles = min(num_ctas, total)
-  long long rem;    // tiles (balanced) or units (explicit) this CTA still owns
-  long long unit;   // explicit: next unit
-  int b, h, ti;     // balanced cursor: sequence, head, first unprocessed tile of the group
-  int len, ntg;     // length and tile count of sequence b
-  long long tiles_before_group;
-  long long rows_before_seq;
+  long long total;     // balanced: units (tiles + group overheads) in the batch; explicit: split units
+  long long n_chunks;  // balanced: M
+  long long parts;     // balanced: CTAs that own chunks (P)
+  // forward scan cursor: first sequence not yet passed, with the sums over earlier ones
+  int sb;
+  long long s_tiles_before, s_rows_before;
+  // unit cursor (balanced)
+  int b, h, ui;   // sequence, head, unit inside the group (overhead units first, then tiles)
+  int len, ntg;   // length and tile count of sequence b
+  int ti;         // tile inside the group (ui - overhead; negative inside the overhead)
+  long long tiles_before_group, rows_before_seq;  // tiles_before_group counts units
+  // explicit mode cursor
+  long long unit;
 
   GQA_HD int len_of(int bb) const {
     int l = p.max_seq;
@@ -83,220 +103,322 @@ struct Walker {
     return l;
   }
   GQA_HD int tiles_of(int l) const { return (l + p.tile_rows - 1) / p.tile_rows; }
-  GQA_HD long long cta_of_tile(long long t) const {
-    // largest c with floor(c*total/parts) <= t.  parts <= total, so every one of the
-    // `parts` ranges is non-empty and a group's CTAs are consecutive.
-    return ((t + 1) * parts - 1) / total;
+  // cost units of one group of a sequence with l keys (0 for an empty sequence)
+  GQA_HD int units_of(int l) const {
+    const int t = tiles_of(l);
+    return t ? t + (p.num_splits > 0 ? 0 : p.group_overhead) : 0;
   }
+  GQA_HD int overhead() const { return p.num_splits > 0 ? 0 : p.group_overhead; }
 
-  // Finish initialisation once `total`, the starting sequence and the sums over the
-  // sequences before it are known.
-  GQA_HD void seat_balanced(long long t0, long long t1, int b0, long long tiles_before,
-                            long long rows_before) {
-    rem = t1 - t0;
-    b = b0;
-    h = 0;
-    ti = 0;
-    len = 0;
-    ntg = 0;
-    tiles_before_group = tiles_before;
-    rows_before_seq = rows_before;
-    if (rem <= 0 || b0 >= p.batch) {
-      rem = 0;
-      return;
-    }
-    len = len_of(b);
-    ntg = tiles_of(len);
-    long long off = t0 - tiles_before;
-    h = (int)(off / ntg);
-    ti = (int)(off % ntg);
-    tiles_before_group = tiles_before + (long long)h * ntg;
-  }
-
-  // Serial initialisation: usable from host code or from a single device thread.
-  GQA_HD void init_serial(const SchedParams& sp, int cta_index) {
-    p = sp;
-    cta = cta_index;
+  // ---- geometry ---------------------------------------------------------------
+  GQA_HD void set_geometry(long long total_items) {
+    total = total_items;
+    sb = 0;
+    s_tiles_before = s_rows_before = 0;
+    b = h = ui = ti = len = ntg = 0;
+    tiles_before_group = rows_before_seq = 0;
     unit = 0;
     if (p.num_splits > 0) {
-      total = (long long)p.batch * p.num_kv_heads * p.num_splits;
-      unit = cta * total / p.num_ctas;
-      rem = (cta + 1) * total / p.num_ctas - unit;
-      b = (int)(unit / p.num_splits / p.num_kv_heads);
+      n_chunks = total;
       parts = p.num_ctas;
-      rows_before_seq = 0;
-      for (int bb = 0; bb < b && bb < p.batch; ++bb) rows_before_seq += len_of(bb);
-      h = ti = len = ntg = 0;
-      tiles_before_group = 0;
+      return;
+    }
+    const long long c = p.chunk_tiles > 0 ? p.chunk_tiles : 1;
+    n_chunks = (total + c - 1) / c;
+    parts = n_chunks < p.num_ctas ? n_chunks : p.num_ctas;
+  }
+  GQA_HD long long chunk_tiles() const { return p.chunk_tiles > 0 ? p.chunk_tiles : 1; }
+  // chunk (balanced) or unit (explicit) range owned by CTA c
+  GQA_HD void cta_range(int c, long long& q0, long long& q1) const {
+    if (p.num_splits > 0) {
+      q0 = c * total / p.num_ctas;
+      q1 = (c + 1) * total / p.num_ctas;
+    } else if (c < parts) {
+      q0 = c * n_chunks / parts;
+      q1 = (c + 1) * n_chunks / parts;
+    } else {
+      q0 = q1 = 0;
+    }
+  }
+  // owner of chunk q: largest c with floor(c*M/P) <= q (P <= M: every owner has chunks)
+  GQA_HD long long cta_of_chunk(long long q) const { return ((q + 1) * parts - 1) / n_chunks; }
+  GQA_HD void chunk_tile_range(long long q, long long& t0, long long& t1) const {
+    t0 = q * chunk_tiles();
+    t1 = t0 + chunk_tiles();
+    if (t1 > total) t1 = total;
+  }
+  GQA_HD long long group_index() const { return (long long)b * p.num_kv_heads + h; }
+  GQA_HD long long kv_row0() const {
+    return p.layout == kLayoutPadded ? group_index() * (long long)p.max_seq
+                                     : rows_before_seq * p.num_kv_heads + (long long)h * len;
+  }
+  // slot bookkeeping of the current group (balanced)
+  // (measured from the group's first tile unit: chunks that only hold its overhead produce
+  // no partial)
+  GQA_HD long long group_first_tile_unit() const { return tiles_before_group + overhead(); }
+  GQA_HD int group_first_slot() const {
+    return (int)(group_first_tile_unit() / chunk_tiles() + group_index());
+  }
+  GQA_HD int group_static_parts() const {
+    const long long c = chunk_tiles();
+    return (int)(cta_of_chunk((group_first_tile_unit() + ntg - 1) / c) -
+                 cta_of_chunk(group_first_tile_unit() / c) + 1);
+  }
+  GQA_HD int group_static_index(int cta) const {
+    return (int)(cta - cta_of_chunk(group_first_tile_unit() / chunk_tiles()));
+  }
+
+  // ---- positioning on unit t0 of the line (balanced) ---------------------------------
+  GQA_HD void seat(long long t0) {
+    b = sb;
+    h = ui = len = ntg = 0;
+    ti = -overhead();
+    tiles_before_group = s_tiles_before;
+    rows_before_seq = s_rows_before;
+    if (sb >= p.batch) return;
+    len = len_of(b);
+    ntg = tiles_of(len);
+    const int ung = ntg + overhead();
+    const long long off = t0 - s_tiles_before;
+    h = (int)(off / ung);
+    ui = (int)(off % ung);
+    ti = ui - overhead();
+    tiles_before_group = s_tiles_before + (long long)h * ung;
+  }
+  GQA_HD void rewind_if_behind(long long t0) {
+    if (t0 < s_tiles_before) {
+      sb = 0;
+      s_tiles_before = s_rows_before = 0;
+    }
+  }
+  // advance the cursor by one unit; returns false when the line is exhausted
+  GQA_HD bool advance() {
+    ++ti;
+    if (++ui < ntg + overhead()) return true;
+    tiles_before_group += ntg + overhead();
+    ui = 0;
+    ti = -overhead();
+    if (++h < p.num_kv_heads) return true;
+    h = 0;
+    rows_before_seq += len;
+    ++b;
+    len = ntg = 0;
+    while (b < p.batch) {
+      len = len_of(b);
+      ntg = tiles_of(len);
+      if (ntg) return true;
+      ++b;
+    }
+    return false;
+  }
+
+  // Serial versions: usable from host code or from a single device thread.
+  GQA_HD void init_serial(const SchedParams& sp) {
+    p = sp;
+    if (p.num_splits > 0) {
+      set_geometry((long long)p.batch * p.num_kv_heads * p.num_splits);
       return;
     }
     long long n = 0;
-    for (int bb = 0; bb < p.batch; ++bb) n += tiles_of(len_of(bb));
-    total = n * p.num_kv_heads;
-    parts = total < p.num_ctas ? total : p.num_ctas;
-    long long t0 = 0, t1 = 0;
-    if (cta < parts) {
-      t0 = cta * total / parts;
-      t1 = (cta + 1) * total / parts;
+    for (int bb = 0; bb < p.batch; ++bb) n += units_of(len_of(bb));
+    set_geometry(n * p.num_kv_heads);
+  }
+  GQA_HD void seek_serial(long long t0) {
+    rewind_if_behind(t0);
+    for (; sb < p.batch; ++sb) {
+      const int l = len_of(sb);
+      const long long nt = (long long)units_of(l) * p.num_kv_heads;
+      if (s_tiles_before + nt > t0) break;
+      s_tiles_before += nt;
+      s_rows_before += l;
     }
-    long long acc_t = 0, acc_r = 0;
-    int b0 = 0;
-    for (; b0 < p.batch; ++b0) {
-      int l = len_of(b0);
-      long long nt = (long long)tiles_of(l) * p.num_kv_heads;
-      if (acc_t + nt > t0) break;
-      acc_t += nt;
-      acc_r += l;
-    }
-    seat_balanced(t0, t1, b0, acc_t, acc_r);
+    seat(t0);
+  }
+  // explicit mode: position on unit u (units are visited in increasing order)
+  GQA_HD void seek_unit_serial(long long u) {
+    unit = u;
+    const int nb = (int)(u / p.num_splits / p.num_kv_heads);
+    for (; sb < nb && sb < p.batch; ++sb) s_rows_before += len_of(sb);
+    b = sb;
+    rows_before_seq = s_rows_before;
   }
 
 #if defined(__CUDACC__)
-  // Warp-cooperative initialisation: all 32 lanes of a warp call it together and end
-  // with identical state.  Lengths are read 32 at a time and combined with shuffles,
-  // so the cost is a few dependent L2 reads even for batches of thousands.
-  __device__ __forceinline__ void init_warp(const SchedParams& sp, int cta_index) {
+  // Warp-cooperative versions: all 32 lanes of a warp call them together and end with
+  // identical state.  Lengths are read 32 at a time and combined with shuffles.
+  __device__ __forceinline__ void init_warp(const SchedParams& sp) {
     p = sp;
-    cta = cta_index;
-    unit = 0;
-    const int lane = threadIdx.x & 31;
-    const unsigned full = 0xffffffffu;
     if (p.num_splits > 0) {
-      total = (long long)p.batch * p.num_kv_heads * p.num_splits;
-      unit = cta * total / p.num_ctas;
-      rem = (cta + 1) * total / p.num_ctas - unit;
-      b = (int)(unit / p.num_splits / p.num_kv_heads);
-      parts = p.num_ctas;
-      long long r = 0;
-      for (int bb = lane; bb < b && bb < p.batch; bb += 32) r += len_of(bb);
-      for (int o = 16; o; o >>= 1) r += __shfl_xor_sync(full, r, o);
-      rows_before_seq = r;
-      h = ti = len = ntg = 0;
-      tiles_before_group = 0;
+      set_geometry((long long)p.batch * p.num_kv_heads * p.num_splits);
       return;
     }
+    const int lane = threadIdx.x & 31;
     long long n = 0;
-    for (int bb = lane; bb < p.batch; bb += 32) n += tiles_of(len_of(bb));
-    for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(full, n, o);
-    total = n * p.num_kv_heads;
-    parts = total < p.num_ctas ? total : p.num_ctas;
-    long long t0 = 0, t1 = 0;
-    if (cta < parts) {
-      t0 = cta * total / parts;
-      t1 = (cta + 1) * total / parts;
-    }
-    long long acc_t = 0, acc_r = 0;
-    int b0 = p.batch;
-    for (int base = 0; base < p.batch; base += 32) {
-      int bb = base + lane;
-      int l = bb < p.batch ? len_of(bb) : 0;
-      long long nt = (long long)tiles_of(l) * p.num_kv_heads;
+    for (int bb = lane; bb < p.batch; bb += 32) n += units_of(len_of(bb));
+    for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    set_geometry(n * p.num_kv_heads);
+  }
+  __device__ __forceinline__ void seek_warp(long long t0) {
+    const int lane = threadIdx.x & 31;
+    const unsigned full = 0xffffffffu;
+    rewind_if_behind(t0);
+    while (sb < p.batch) {
+      const int bb = sb + lane;
+      const int l = bb < p.batch ? len_of(bb) : 0;
+      const long long nt = (long long)units_of(l) * p.num_kv_heads;
       long long it = nt, ir = l;  // inclusive scans over the 32 lanes
       for (int o = 1; o < 32; o <<= 1) {
-        long long a = __shfl_up_sync(full, it, o);
-        long long c = __shfl_up_sync(full, ir, o);
+        const long long a = __shfl_up_sync(full, it, o);
+        const long long c = __shfl_up_sync(full, ir, o);
         if (lane >= o) {
           it += a;
           ir += c;
         }
       }
-      unsigned hit = __ballot_sync(full, bb < p.batch && acc_t + it > t0);
+      const unsigned hit = __ballot_sync(full, bb < p.batch && s_tiles_before + it > t0);
       if (hit) {
-        int first = __ffs(hit) - 1;
-        long long et = __shfl_sync(full, it - nt, first);
-        long long er = __shfl_sync(full, ir - l, first);
-        acc_t += et;
-        acc_r += er;
-        b0 = base + first;
+        const int first = __ffs(hit) - 1;
+        s_tiles_before += __shfl_sync(full, it - nt, first);
+        s_rows_before += __shfl_sync(full, ir - l, first);
+        sb += first;
         break;
       }
-      acc_t += __shfl_sync(full, it, 31);
-      acc_r += __shfl_sync(full, ir, 31);
+      s_tiles_before += __shfl_sync(full, it, 31);
+      s_rows_before += __shfl_sync(full, ir, 31);
+      sb += 32;
     }
-    seat_balanced(t0, t1, b0, acc_t, acc_r);
+    if (sb > p.batch) sb = p.batch;
+    seat(t0);
+  }
+  __device__ __forceinline__ void seek_unit_warp(long long u) {
+    const int lane = threadIdx.x & 31;
+    unit = u;
+    const int nb = (int)(u / p.num_splits / p.num_kv_heads);
+    long long r = 0;
+    for (int bb = sb + lane; bb < nb && bb < p.batch; bb += 32) r += len_of(bb);
+    for (int o = 16; o; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    s_rows_before += r;
+    if (nb > sb) sb = nb < p.batch ? nb : p.batch;
+    b = sb;
+    rows_before_seq = s_rows_before;
   }
 #endif
 
-  // Produce the next segment of this CTA.  Called by single threads; no cross-lane ops.
-  GQA_HD bool next(Segment& s) {
-    if (rem <= 0) return false;
-    const int T = p.tile_rows;
-    if (p.num_splits > 0) {
-      const int K = p.num_splits;
-      long long g = unit / K;
-      int sp = (int)(unit % K);
-      int nb = (int)(g / p.num_kv_heads);
-      while (b < nb) {
-        rows_before_seq += len_of(b);
-        ++b;
-      }
-      h = (int)(g % p.num_kv_heads);
-      len = len_of(b);
-      ntg = tiles_of(len);
-      int cs = (ntg + K - 1) / K;
-      long long tb = (long long)sp * cs;
-      if (tb > ntg) tb = ntg;
-      long long te = tb + cs;
-      if (te > ntg) te = ntg;
-      s.b = b;
-      s.h = h;
-      s.len = len;
-      long long re = te * T;
-      s.row_begin = tb == te ? 0 : (int)(tb * T);  // an empty chunk is reported as [0, 0)
-      s.row_end = tb == te ? 0 : (int)(re < len ? re : len);
-      s.slot = (int)unit;
-      s.first_slot = (int)(g * K);
-      s.n_parts = K;
-      s.kv_row0 = p.layout == kLayoutPadded ? g * (long long)p.max_seq
-                                            : rows_before_seq * p.num_kv_heads + (long long)h * len;
-      ++unit;
-      --rem;
-      return true;
+  // explicit mode: describe unit `unit` and move to the next one
+  GQA_HD void next_unit(Segment& s) {
+    const int T = p.tile_rows, K = p.num_splits;
+    const long long g = unit / K;
+    const int sp = (int)(unit % K);
+    const int nb = (int)(g / p.num_kv_heads);
+    while (b < nb) {
+      rows_before_seq += len_of(b);
+      ++b;
     }
-    long long take = ntg - ti;
-    if (take > rem) take = rem;
-    long long g = (long long)b * p.num_kv_heads + h;
+    h = (int)(g % p.num_kv_heads);
+    len = len_of(b);
+    ntg = tiles_of(len);
+    const int cs = (ntg + K - 1) / K;
+    long long tb = (long long)sp * cs;
+    if (tb > ntg) tb = ntg;
+    long long te = tb + cs;
+    if (te > ntg) te = ntg;
     s.b = b;
     s.h = h;
     s.len = len;
-    s.row_begin = ti * T;
-    long long re = (long long)(ti + take) * T;
-    s.row_end = (int)(re < len ? re : len);
-    long long cf = cta_of_tile(tiles_before_group);
-    long long cl = cta_of_tile(tiles_before_group + ntg - 1);
-    s.n_parts = (int)(cl - cf + 1);
-    s.first_slot = (int)(cf + g);
-    s.slot = (int)(cta + g);
-    s.kv_row0 = p.layout == kLayoutPadded ? g * (long long)p.max_seq
-                                          : rows_before_seq * p.num_kv_heads + (long long)h * len;
-    rem -= take;
-    ti += (int)take;
-    if (ti == ntg) {
-      tiles_before_group += ntg;
-      ti = 0;
-      if (++h == p.num_kv_heads) {
-        h = 0;
-        rows_before_seq += len;
-        ++b;
-        len = 0;
-        ntg = 0;
-        while (b < p.batch) {
-          len = len_of(b);
-          ntg = tiles_of(len);
-          if (ntg) break;
-          ++b;
-        }
-        if (b >= p.batch) rem = 0;
-      }
+    const long long re = te * T;
+    s.row_begin = tb == te ? 0 : (int)(tb * T);  // an empty piece is reported as [0, 0)
+    s.row_end = tb == te ? 0 : (int)(re < len ? re : len);
+    s.slot = (int)unit;
+    s.first_slot = (int)(g * K);
+    s.n_parts = K;
+    s.kv_row0 = kv_row0();
+    ++unit;
+  }
+
+  // Static schedule of CTA `cta` (no stealing), for inspection and tests.  Call
+  // static_range() for the tile / unit range, seek to its start (serial or warp
+  // version), then walk_static() fills `out` with up to `cap` segments and returns how
+  // many the CTA has.
+  GQA_HD bool static_range(int cta, long long& t0, long long& t1) const {
+    long long q0, q1;
+    cta_range(cta, q0, q1);
+    if (q0 >= q1) return false;
+    if (p.num_splits > 0) {
+      t0 = q0;
+      t1 = q1;
+    } else {
+      long long tmp;
+      chunk_tile_range(q0, t0, tmp);
+      chunk_tile_range(q1 - 1, tmp, t1);
     }
     return true;
   }
+  GQA_HD long long walk_static(int cta, long long t0, long long t1, Segment* out, long long cap) {
+    long long n = 0;
+    if (p.num_splits > 0) {
+      for (long long u = t0; u < t1; ++u, ++n) {
+        Segment s;
+        next_unit(s);
+        if (n < cap) out[n] = s;
+      }
+      return n;
+    }
+    long long t = t0;
+    while (t < t1) {
+      if (ti < 0) {  // inside the group's overhead: no tile, nothing to report
+        ++t;
+        if (!advance()) break;
+        continue;
+      }
+      long long take = ntg - ti;
+      if (take > t1 - t) take = t1 - t;
+      Segment s;
+      s.b = b;
+      s.h = h;
+      s.len = len;
+      s.row_begin = ti * p.tile_rows;
+      const long long re = (long long)(ti + take) * p.tile_rows;
+      s.row_end = (int)(re < len ? re : len);
+      s.kv_row0 = kv_row0();
+      s.first_slot = group_first_slot();
+      s.n_parts = group_static_parts();
+      s.slot = s.first_slot + group_static_index(cta);
+      if (n < cap) out[n] = s;
+      ++n;
+      t += take;
+      ui += (int)take - 1;
+      ti += (int)take - 1;
+      if (!advance()) break;
+    }
+    return n;
+  }
 };
 
-// Upper bound on partial slots for a launch.
-GQA_HD long long max_slots(int batch, int num_kv_heads, int num_ctas, int num_splits) {
-  long long groups = (long long)batch * num_kv_heads;
-  return num_splits > 0 ? groups * num_splits : groups + num_ctas;
+// Upper bound on partial slots for a launch with chunk size `chunk_tiles`:
+// one slot per chunk plus one per group.
+GQA_HD long long max_slots(long long groups, int num_splits, long long max_units_per_group,
+                           int chunk_tiles) {
+  if (num_splits > 0) return groups * num_splits;
+  const long long tiles = groups * max_units_per_group;
+  return (tiles + chunk_tiles - 1) / chunk_tiles + groups + 1;
+}
+
+// Chunk size (tiles) for the balanced schedule: small enough that stealing evens out the
+// tail (about 48 chunks per CTA, 4 to 16 tiles each), never more chunks than `slot_budget` allows.
+GQA_HD int choose_chunk_tiles(long long groups, long long max_units_per_group, int num_ctas,
+                              long long slot_budget) {
+  const long long tiles = groups * max_units_per_group;
+  // at least 4 tiles (about 3 us of streaming on one SM) so that the atomic that hands out
+  // a chunk stays off the critical path
+  long long c = tiles / ((long long)num_ctas * 48);
+  if (c < 4) c = 4;
+  if (c > 16) c = 16;
+  const long long room = slot_budget - groups - 1;
+  if (room > 0) {
+    const long long need = (tiles + room - 1) / room;  // smallest chunk that fits the budget
+    if (c < need) c = need;
+  }
+  return (int)c;
 }
 
 }  // namespace gqa

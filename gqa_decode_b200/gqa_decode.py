@@ -171,6 +171,7 @@ def gqa_decode_attention_batched(
     max_seq_len: Optional[int] = None,
     num_kv_heads: Optional[int] = None,
     fp8_exact_v: bool = False,
+    work_stealing: bool = False,
     _entry: str = "auto",
     _no_merge: bool = False,
     _plan_only: bool = False,
@@ -187,6 +188,10 @@ def gqa_decode_attention_batched(
     ``[B, Hkv]`` (per sequence and KV head, the reference's fp8_utils scheme).
     num_splits: ``None`` = balanced persistent schedule; ``K`` = K partials per
       (sequence, KV head).
+    work_stealing: let CTAs that finish their static share steal work chunks from others
+      (helps when SMs are shared with other work; makes the float32 summation order, hence
+      the last bits of the result, depend on timing).  Default: static shares, results are
+      bit-reproducible.
     fp8_exact_v: round every dequantised V element to the 16-bit type as
       ``dequantize_kv_fp8`` does (K always is); default applies the V scale to the fp32
       output instead, which is faster and differs only in that rounding.
@@ -244,8 +249,8 @@ def gqa_decode_attention_batched(
         raise ValueError("num_q_heads must be divisible by num_kv_heads")
     if num_q_heads // num_kv_heads > 16:
         raise ValueError("group size must be in [1, 16]")
-    if head_dim not in ((128,) if fp8 else (64, 128)):
-        raise ValueError("head_dim must be 64 or 128 (128 for FP8)")
+    if head_dim not in ((128,) if fp8 else (64, 128, 256)):
+        raise ValueError("head_dim must be 64, 128 or 256 (128 for FP8)")
     if seq_lens is not None:
         if seq_lens.dtype != torch.int32 or seq_lens.device != q.device or seq_lens.numel() != batch:
             raise ValueError("seq_lens must be an int32 CUDA tensor of shape [batch]")
@@ -279,7 +284,8 @@ def gqa_decode_attention_batched(
     a.num_splits, a.num_ctas = splits, num_ctas
     a.flags = (_native.FLAG_SEPARATE_MERGE if separate_merge else 0) | (
         _native.FLAG_NO_MERGE if _no_merge else 0) | (
-        _native.FLAG_FP8_EXACT_V if fp8_exact_v else 0)
+        _native.FLAG_FP8_EXACT_V if fp8_exact_v else 0) | (
+        _native.FLAG_WORK_STEALING if work_stealing else 0)
     a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     a.stream = torch.cuda.current_stream(dev).cuda_stream

@@ -34,6 +34,12 @@ extern "C" {
 /* flags */
 #define GQA_FLAG_SEPARATE_MERGE 1 /* run the merge as a second kernel instead of in-kernel */
 #define GQA_FLAG_NO_MERGE 2       /* explicit splits only: write every partial, merge nothing */
+#define GQA_FLAG_WORK_STEALING 8   /* balanced schedule: CTAs that finish their own share steal work
+                                     chunks from others.  Off by default: on an otherwise idle GPU
+                                     the static shares finish within a few percent of each other;
+                                     useful when SMs are shared with other work.  With it the
+                                     float32 summation order, hence the last bits of the result,
+                                     depend on timing; without it results are bit-reproducible */
 #define GQA_FLAG_FP8_EXACT_V 4    /* E4M3: round every dequantised V element to the 16-bit type like
                                      dequantize_kv_fp8 (gqa_decode/fp8_utils.py:54-55) instead of
                                      applying the V scale once to the fp32 output (default, faster) */
@@ -64,7 +70,7 @@ typedef struct gqa_decode_args {
   int32_t batch;
   int32_t num_q_heads;
   int32_t num_kv_heads;
-  int32_t head_dim;         /* 64 or 128 (E4M3: 128) */
+  int32_t head_dim;         /* 64, 128 or 256 (E4M3: 128) */
   int32_t max_seq_len;      /* rows per head slab (padded layout); bound on every length */
   int64_t total_rows;       /* rows of the whole K (= V) allocation, viewed as [rows, head_dim] */
   int32_t q_dtype;          /* GQA_DTYPE_BF16 | GQA_DTYPE_FP16 */
@@ -85,10 +91,10 @@ int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_k
                                size_t* bytes);
 
 /*
- * Byte offsets inside a workspace of the same arguments: offsets[0] status word,
- * [1] tickets, [2] group table, [3] partial log-sum-exp [slots, G] fp32,
- * [4] partial outputs [slots, G, head_dim] fp32, [5] total bytes.  With explicit splits
- * K, slot = (sequence * Hkv + kv_head) * K + split.  Lets a caller that asked for
+ * Byte offsets inside a workspace for explicit splits (num_splits = K > 0): offsets[0]
+ * status word, [1] tickets, [2] group table, [3] partial log-sum-exp [slots, G] fp32,
+ * [4] partial outputs [slots, G, head_dim] fp32, [5] total bytes;
+ * slot = (sequence * Hkv + kv_head) * K + split.  Lets a caller that asked for
  * GQA_FLAG_NO_MERGE read the partials (the reference's reduction="python" path,
  * gqa_decode/gqa_decode.py:753-756).
  */
@@ -101,7 +107,8 @@ int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_
 int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Copy the status word back (synchronises the stream): 0 = ok, else OR of
- * 1 (consumer wait expired), 2 (producer wait expired), 4 (shared-memory misalignment). */
+ * 1 (consumer wait expired), 2 (producer wait expired), 4 (shared-memory misalignment),
+ * 8 (a partial-slot index was out of range: the control words were not clean). */
 int gqa_decode_read_status(const void* workspace, void* stream, int32_t* status);
 
 /* bf16 / fp16 K and V.  Replaces gqa_decode_attention, gqa_decode/gqa_decode.py:672-762
@@ -127,15 +134,16 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
  *
  * What it does: identical inputs, outputs and arithmetic to gqa_decode_attention
  * (bf16/fp16 K and V, any schedule), but the partials, tickets and status word live in a
- * fixed array of GQA_STATIC_SCRATCH_BYTES that is part of the library image; every GPU
+ * fixed array of GQA_STATIC_SCRATCH_BYTES (16 MiB) that is part of the library image; every GPU
  * that loads the library keeps that much memory until the process exits.  args->workspace
  * and args->workspace_bytes are ignored.  The call performs no cudaMalloc, cudaFree or
  * any other allocation.
  *
  * Limits and rules:
- *  - if the launch needs more scratch than GQA_STATIC_SCRATCH_BYTES (see
- *    gqa_decode_workspace_bytes; roughly (batch*Hkv + #SMs) * G * (D+1) * 4 bytes for the
- *    balanced schedule) the call returns GQA_ERR_LIMIT and launches nothing;
+ *  - if the launch cannot fit the array (explicit splits need batch*Hkv*K partial slots of
+ *    G*(D+1)*4 bytes each, the balanced schedule at least batch*Hkv + 2 of them and uses
+ *    coarser work chunks when room is short) the call returns GQA_ERR_LIMIT and launches
+ *    nothing;
  *  - the first call on each device looks up the array's device address (once per
  *    device, with that device current); make that first call during set-up, before any
  *    stream capture is begun;
@@ -146,7 +154,7 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
  *  - gqa_decode_read_status cannot be pointed at the array; a caller that wants the
  *    status word uses the workspace-taking entry instead.
  */
-#define GQA_STATIC_SCRATCH_BYTES (8u << 20)
+#define GQA_STATIC_SCRATCH_BYTES (16u << 20)
 int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args);
 
 /* E4M3 K and V with per-(sequence, KV head) fp32 scales.  Replaces
@@ -192,6 +200,12 @@ int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num
                              int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
                              int32_t num_splits, int32_t kv_layout, int64_t* records,
                              int64_t capacity, int64_t* count, void* stream);
+
+/* Diagnostics: while a non-NULL device buffer of 3 * num_ctas uint64 is registered, every
+ * decode launch of this process writes per CTA {start, first tile landed, end} as
+ * %globaltimer nanoseconds into it (used to study launch ramp and tail).  NULL switches
+ * it off.  Not thread-safe with concurrent launches. */
+int gqa_debug_set_timestamp_buffer(uint64_t* device_buffer);
 
 /* Library version string. */
 const char* gqa_decode_version(void);

@@ -39,7 +39,7 @@ def test_struct_matches_header_fields():
 def test_host_only_entries(native_lib):
     assert b"sm_100a" in native_lib.gqa_decode_version()
     assert native_lib.gqa_decode_tile_rows(128, 0) == 64
-    assert native_lib.gqa_decode_tile_rows(128, 2) == 128
+    assert native_lib.gqa_decode_tile_rows(128, 2) == 256
     assert native_lib.gqa_decode_tile_rows(96, 0) < 0
     n = ctypes.c_size_t(0)
     assert native_lib.gqa_decode_workspace_bytes(16, 32, 8, 128, 0, 148, ctypes.byref(n)) == 0

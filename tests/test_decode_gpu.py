@@ -109,6 +109,16 @@ def test_group_of_sixteen_and_fp16(G):
         _check(G, out, O.attend_one_sequence(q, k, v), O.attend_one_sequence_f64(q, k, v))
 
 
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (24, 2)])
+def test_head_dim_256(G, hq, hkv):
+    """head_dim 256 (accepted by the reference's bf16 kernels, gqa_decode/gqa_decode.py:109-112)."""
+    g = torch.Generator().manual_seed(256 + hq)
+    for dt in (torch.bfloat16, torch.float16):
+        q, k, v = O.randn_bf16((hq, 256), g, dt), O.randn_bf16((hkv, 1500, 256), g, dt), O.randn_bf16((hkv, 1500, 256), g, dt)
+        out = G.gqa_decode_attention(q.to(DEV), k.to(DEV), v.to(DEV))
+        _check(G, out, O.attend_one_sequence(q, k, v), O.attend_one_sequence_f64(q, k, v))
+
+
 def test_peaked_softmax_and_large_scores(G):
     """One key dominates (score gap ~ 40): the running-max rescale must not lose it or overflow."""
     g = torch.Generator().manual_seed(21)
@@ -300,3 +310,27 @@ def test_plan_and_cuda_graph_replay(G):
     torch.cuda.synchronize()
     assert torch.equal(plan.result, want2)
     assert G.read_status() == 0
+
+
+def test_work_stealing_matches_static_schedule(G):
+    """With work_stealing=True idle CTAs steal chunks; the result may differ from the
+    default static schedule only by float32 summation order (far below one bf16 ulp), and
+    the static schedule is bit-reproducible."""
+    g = torch.Generator().manual_seed(31)
+    lens = [9000, 1, 4097, 7, 30000, 64, 12345, 0]
+    smax = max(lens)
+    q = O.randn_bf16((len(lens), 32, 128), g).to(DEV)
+    k = O.randn_bf16((len(lens), 8, smax, 128), g).to(DEV)
+    v = O.randn_bf16((len(lens), 8, smax, 128), g).to(DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    a, a32 = G.gqa_decode_attention_batched(q, k, v, sl, return_f32=True)
+    b, b32 = G.gqa_decode_attention_batched(q, k, v, sl, return_f32=True)
+    assert torch.equal(a, b) and torch.equal(a32, b32)
+    for _ in range(5):
+        c, c32 = G.gqa_decode_attention_batched(q, k, v, sl, return_f32=True, work_stealing=True)
+        assert float((c32 - a32).abs().max()) < 2e-5 * max(1.0, float(a32.abs().max())), float((c32 - a32).abs().max())
+        assert G.read_status() == 0
+    ref = torch.stack([
+        O.attend_one_sequence(q[i].cpu(), k[i, :, :l].cpu(), v[i, :, :l].cpu()) if l
+        else torch.zeros(32, 128, dtype=torch.bfloat16) for i, l in enumerate(lens)])
+    _check(G, c, ref)

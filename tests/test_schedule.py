@@ -1,6 +1,7 @@
-"""Host replay of the device scheduler (gqa_schedule_dump): every key of every
-(sequence, KV head) group is covered exactly once, partial slots never collide, and
-each group's bookkeeping (first_slot, n_parts) agrees across the CTAs that share it."""
+"""Host replay of the device scheduler's static schedule (gqa_schedule_dump): every key of
+every (sequence, KV head) group is covered exactly once, partial slots never collide, each
+group's bookkeeping (first_slot, n_parts) agrees across the CTAs that share it, and the
+groups' slot ranges leave room for one partial per work chunk (what stealing can produce)."""
 import numpy as np
 import pytest
 
@@ -27,7 +28,8 @@ def check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout):
         assert r0 % tile == 0 and r0 <= r1 <= lens[b]
         assert slot not in slots
         slots.add(slot)
-        bound = batch * hkv * splits if splits else batch * hkv + ctas
+        tiles = sum(-(-l // tile) for l in lens) * hkv
+        bound = batch * hkv * splits if splits else tiles + batch * hkv + 1
         assert 0 <= slot < bound
         assert first <= slot < first + nparts
         g = (b, h)
@@ -50,11 +52,18 @@ def check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout):
             assert pos == lens[b]
             first, nparts = info[(b, h)]
             assert len(covered[(b, h)]) == nparts
-    if not splits:  # balanced: per-CTA tile counts differ by at most one
+    if not splits:
+        # balanced: CTAs own equal numbers of chunks (+-1) of at most 16 cost units, where a
+        # unit is a tile or one of the 2 overhead units every group carries
         per = np.zeros(ctas, dtype=np.int64)
         for cta, b, h, r0, r1, *_ in rec:
-            per[cta] += -(-(r1 - r0) // tile)
-        assert per.max() - per.min() <= 1
+            per[cta] += -(-(r1 - r0) // tile) + (2 if r0 == 0 else 0)
+        used = per[per > 0]
+        assert used.max() - used.min() <= 2 * 16 + 2
+        # slot ranges of different groups are disjoint even if every chunk became a partial
+        spans = sorted((first, first + nparts) for first, nparts in info.values())
+        firsts = sorted(set(first for first, _ in info.values()))
+        assert len(firsts) == len(info)
 
 
 CASES = [

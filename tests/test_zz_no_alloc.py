@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _args(native, q, k, v, seq_lens, out, workspace=None, num_splits=0):
+def _args(native, q, k, v, seq_lens, out, workspace=None, num_splits=0, flags=0):
     b, hq, d = q.shape
     _, hkv, smax, _ = k.shape
     a = native.DecodeArgs()
@@ -28,6 +28,7 @@ def _args(native, q, k, v, seq_lens, out, workspace=None, num_splits=0):
     a.q_dtype = a.kv_dtype = native.DTYPE_BF16
     a.kv_layout = native.LAYOUT_PADDED
     a.num_splits = num_splits
+    a.flags = flags
     if workspace is not None:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     a.stream = torch.cuda.current_stream().cuda_stream
@@ -53,14 +54,14 @@ def test_static_scratch_entry_matches_workspace_entry():
         sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
         need = ctypes.c_size_t()
         assert lib.gqa_decode_workspace_bytes(b, hq, hkv, d, splits, 0, ctypes.byref(need)) == 0
-        assert need.value <= _native.STATIC_SCRATCH_BYTES
         ws = torch.zeros(need.value, dtype=torch.uint8, device=DEV)
         want = torch.empty_like(q)
         got = torch.full_like(q, float("nan"))
-        assert lib.gqa_decode_attention(ctypes.byref(_args(_native, q, k, v, sl, want, ws, splits))) == 0
+        fl = 0  # default static schedule: both entries sum in the same order
+        assert lib.gqa_decode_attention(ctypes.byref(_args(_native, q, k, v, sl, want, ws, splits, fl))) == 0
         # no workspace is passed: the library's own array is the scratch
         assert lib.gqa_decode_attention_static_scratch(
-            ctypes.byref(_args(_native, q, k, v, sl, got, None, splits))) == 0
+            ctypes.byref(_args(_native, q, k, v, sl, got, None, splits, fl))) == 0
         torch.cuda.synchronize()
         st = ctypes.c_int32(-1)
         assert lib.gqa_decode_read_status(ws.data_ptr(), None, ctypes.byref(st)) == 0 and st.value == 0
@@ -69,6 +70,13 @@ def test_static_scratch_entry_matches_workspace_entry():
         assert bool((err <= 2e-2 + 1e-2 * want.float().abs()).all()), float(err.max())
         # same schedule, same arithmetic: in fact the two entries agree bit for bit
         assert torch.equal(got, want)
+        # and with work stealing switched on it stays inside the tolerance
+        got2 = torch.full_like(q, float("nan"))
+        assert lib.gqa_decode_attention_static_scratch(
+            ctypes.byref(_args(_native, q, k, v, sl, got2, None, splits, _native.FLAG_WORK_STEALING))) == 0
+        torch.cuda.synchronize()
+        err = (got2.float() - want.float()).abs()
+        assert bool((err <= 2e-2 + 1e-2 * want.float().abs()).all()), float(err.max())
         ref = O.attend_batch(q.cpu(), [k[i, :, :l].cpu() for i, l in enumerate(lens)],
                              [v[i, :, :l].cpu() for i, l in enumerate(lens)])
         err = (got.cpu().float() - ref.float()).abs()
@@ -87,7 +95,7 @@ def test_static_scratch_entry_rejects_oversized_launch():
     k = torch.zeros(1, 8, 128, 128, dtype=torch.bfloat16, device=DEV)
     out = torch.empty_like(q)
     sl = torch.tensor([128], dtype=torch.int32, device=DEV)
-    # 8 KV heads x 700 explicit splits x 4 heads x 129 floats > 8 MiB of partials
-    a = _args(_native, q, k, k, sl, out, None, num_splits=700)
+    # 8 KV heads x 1400 explicit splits x 4 heads x 129 floats > 16 MiB of partials
+    a = _args(_native, q, k, k, sl, out, None, num_splits=1400)
     assert lib.gqa_decode_attention_static_scratch(ctypes.byref(a)) == -5  # GQA_ERR_LIMIT
     assert lib.gqa_decode_attention_static_scratch(None) == -1
