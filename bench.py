@@ -56,7 +56,8 @@ def make_lengths(seed: int, batch: int = 16, max_len: int = 32768):
 class Workload:
     """Device-resident inputs of one rank plus the callable that runs one step."""
 
-    def __init__(self, name: str, rank: int, world: int, dev: torch.device, batch: int = 16):
+    def __init__(self, name: str, rank: int, world: int, dev: torch.device, batch: int = 16,
+                 exchange: str = "nvlink"):
         import gqa_decode_b200 as G
 
         self.G, self.name, self.rank, self.world, self.dev = G, name, rank, world, dev
@@ -158,6 +159,12 @@ class Workload:
         esz = 1 if self.fp8 else 2
         self.bytes_per_step = 2 * hkv_local * sum(self.lens) * d * esz  # this rank, K + V only
         self.step_index = 0
+        self.exchange = None
+        if name == "seqshard" and world > 1 and exchange == "nvlink":
+            from gqa_decode_b200.distributed import NvlinkExchange
+
+            self.exchange = NvlinkExchange(hq, d, dev)
+            self.collective = "fused NVLink push + flag + merge kernel (peer stores, symmetric memory)"
         if name == "seqshard" and world > 1:
             import torch.distributed as dist
 
@@ -195,6 +202,8 @@ class Workload:
             return self.plans[i].result
         if self.name == "seqshard" and self.world > 1:
             _, o32, lse = self.plan.run()
+            if self.exchange is not None:
+                return self.exchange.merge(o32[0], lse[0], torch.bfloat16)
             self.dist.all_gather_into_tensor(self.gather_o, o32[0])
             self.dist.all_gather_into_tensor(self.gather_l, lse[0])
             w = self.world
@@ -344,6 +353,8 @@ def main():
                          "state (0 for profiler runs).  Kept short: after about 0.3 s of continuous "
                          "streaming the B200s of this pool settle about 8 %% below their burst "
                          "bandwidth, and the roofline peak in MEASURED_PEAKS.json is a burst figure")
+    ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
+                    help="seqshard at N>1: fused peer-store exchange+merge kernel, or NCCL all-gather + merge")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -395,7 +406,7 @@ def main():
     _native.load()
     import gqa_decode_b200 as G
 
-    wl = Workload(args.workload, rank, world, dev, args.batch)
+    wl = Workload(args.workload, rank, world, dev, args.batch, args.exchange)
     wl.prepare()
     sampler = ClockSampler(local_rank)
 

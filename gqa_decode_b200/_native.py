@@ -63,6 +63,11 @@ SIGNATURES = {
         ctypes.c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p,
          c_void_p]),
+    "gqa_exchange_buffer_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
+    "gqa_exchange_merge": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_void_p, c_int32, c_int32, ctypes.c_uint32, c_int64, c_int32,
+         c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gqa_select_num_splits": (ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "gqa_schedule_dump": (
         c_int64,

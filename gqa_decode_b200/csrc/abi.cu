@@ -10,6 +10,7 @@
 
 #include "decode_kernel.cuh"
 #include "fp8_path.cuh"
+#include "exchange.cuh"
 
 namespace gqa {
 
@@ -583,6 +584,43 @@ int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num
     merge_rows_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
         o_parts, lse_parts, num_parts, rows, head_dim, static_cast<__nv_bfloat16*>(out), out_f32,
         out_lse);
+  return (int)cudaGetLastError();
+}
+
+size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim) {
+  if (world <= 0 || rows <= 0 || head_dim <= 0) return 0;
+  return exchange_buffer_bytes(world, rows, head_dim);
+}
+
+int gqa_exchange_merge(const float* local_o, const float* local_lse, void* const* peer_bufs,
+                       int32_t rank, int32_t world, uint32_t epoch, int64_t rows,
+                       int32_t head_dim, void* out, int32_t out_dtype, float* out_f32,
+                       float* out_lse, int32_t* status, void* stream) {
+  if (!local_o || !local_lse || !peer_bufs || world <= 0 || world > kExchangeThreads ||
+      rank < 0 || rank >= world || epoch == 0 || rows <= 0 || head_dim <= 0 || head_dim % 4 ||
+      (!out && !out_f32))
+    return GQA_ERR_ARG;
+  if (!aligned16(local_o) || !aligned16(out) || !aligned16(out_f32)) return GQA_ERR_ARG;
+  if (out && out_dtype != GQA_DTYPE_BF16 && out_dtype != GQA_DTYPE_FP16) return GQA_ERR_SHAPE;
+  ExchangeParams p;
+  p.local_o = local_o;
+  p.local_lse = local_lse;
+  p.peer_bufs = peer_bufs;
+  p.rank = rank;
+  p.world = world;
+  p.epoch = epoch;
+  p.rows = rows;
+  p.D = head_dim;
+  p.out = out;
+  p.out_fp16 = out_dtype == GQA_DTYPE_FP16;
+  p.out_f32 = out_f32;
+  p.out_lse = out_lse;
+  p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == GQA_DTYPE_FP16)
+    exchange_merge_kernel<__half><<<world, kExchangeThreads, 0, st>>>(p);
+  else
+    exchange_merge_kernel<__nv_bfloat16><<<world, kExchangeThreads, 0, st>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -51,6 +51,64 @@ def _native_merge(o_parts, lse_parts, out_dtype):
     return merge_partials(o_parts, lse_parts, out_dtype=out_dtype)
 
 
+class NvlinkExchange:
+    """Symmetric receive buffers + the fused push/merge kernel (``gqa_exchange_merge``) for
+    sequence-sharded decode: one kernel per rank replaces two NCCL all-gathers and a merge
+    launch.  Collective constructor: every rank of ``group`` must create it with the same
+    ``rows`` (= batch * num_q_heads) and ``head_dim``.  Ranks must be separate processes on
+    separate GPUs of one NVLink domain.  Plain peer loads/stores only (no multicast)."""
+
+    def __init__(self, rows: int, head_dim: int, device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _native
+
+        self._lib = _native.load()
+        self._native = _native
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.rows, self.head_dim = int(rows), int(head_dim)
+        self.device = torch.device(device)
+        nbytes = int(self._lib.gqa_exchange_buffer_bytes(self.world, self.rows, self.head_dim))
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()  # flags start at 0; epochs start at 1
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every buffer is zeroed before anybody pushes into it
+        self._ctypes = ctypes
+
+    def merge(self, o32: torch.Tensor, lse: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """o32 ``[rows, D]`` float32 and lse ``[rows]`` float32: this rank's partial.  Returns
+        the merged ``[rows, D]`` in ``out_dtype`` (same on every rank)."""
+        n = self._native
+        o32, lse = o32.contiguous(), lse.contiguous()
+        if o32.numel() != self.rows * self.head_dim or lse.numel() != self.rows:
+            raise ValueError("partial does not match the exchange's rows/head_dim")
+        if out is None:
+            out = torch.empty(self.rows, self.head_dim, dtype=out_dtype, device=self.device)
+        f32 = out.dtype == torch.float32
+        self.epoch += 1
+        code = {torch.bfloat16: n.DTYPE_BF16, torch.float16: n.DTYPE_FP16}.get(out.dtype, 0)
+        n.check(
+            self._lib.gqa_exchange_merge(
+                o32.data_ptr(), lse.data_ptr(), self.handle.buffer_ptrs_dev, self.rank, self.world,
+                self.epoch, self.rows, self.head_dim, None if f32 else out.data_ptr(), code,
+                out.data_ptr() if f32 else None, None, self.status.data_ptr(),
+                torch.cuda.current_stream(self.device).cuda_stream),
+            "gqa_exchange_merge")
+        return out
+
+    def check(self) -> int:
+        """Synchronise and return the status word (0 = ok, 16 = a peer never arrived)."""
+        return int(self.status.item())
+
+
 def sequence_sharded_decode(
     q: torch.Tensor,
     k_shard: torch.Tensor,
@@ -60,9 +118,13 @@ def sequence_sharded_decode(
     group: Optional[dist.ProcessGroup] = None,
     local_fn: Callable = _native_local,
     merge_fn: Callable = _native_merge,
+    exchange: Optional["NvlinkExchange"] = None,
     **kw,
 ) -> torch.Tensor:
     """Decode step when every rank holds a contiguous slice of each sequence's keys.
+
+    With ``exchange`` (an :class:`NvlinkExchange`) the partials travel by peer stores inside
+    one fused push+merge kernel; otherwise by one NCCL all-gather followed by the merge kernel.
 
     q ``[B, Hq, D]`` (identical on all ranks); k_shard/v_shard ``[B, Hkv, S_r, D]`` (this
     rank's keys; ``seq_lens_shard`` gives how many of them are valid, 0 allowed).
@@ -73,6 +135,8 @@ def sequence_sharded_decode(
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     o32, lse = local_fn(q, k_shard, v_shard, seq_lens_shard, **kw)
     b, hq, d = o32.shape
+    if exchange is not None:
+        return exchange.merge(o32.reshape(b * hq, d), lse.reshape(b * hq), q.dtype).view(b, hq, d)
     if world == 1:
         return merge_fn(o32.reshape(1, b * hq, d), lse.reshape(1, b * hq), q.dtype).view(b, hq, d)
     # one message per rank: [B*Hq, D+1] = normalised output with its log-sum-exp appended

@@ -173,6 +173,24 @@ int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num
                        int64_t rows, int32_t head_dim, void* out, int32_t out_dtype,
                        float* out_f32, float* out_lse, void* stream);
 
+/*
+ * Sequence-shard exchange over NVLink, fused with the merge (no counterpart in the
+ * reference, which is single-GPU): every rank calls this once per decode step after its
+ * local kernel wrote (local_o [rows, head_dim] fp32, local_lse [rows]).  peer_bufs is a
+ * DEVICE array of `world` pointers: the receive buffer of every rank as mapped into this
+ * process (symmetric memory of gqa_exchange_buffer_bytes() bytes, zero-filled once when
+ * created).  The kernel pushes the local partial to all peers with plain peer stores,
+ * signals them, waits (bounded, 2 s) for all peers' partials and writes the merged
+ * out / out_f32 / out_lse.  `epoch` must be > 0 and increase by one on every call, on all
+ * ranks alike.  `status` (optional device word) gets bit 16 if a peer never arrived.
+ * All ranks must be separate processes on separate GPUs of one NVLink domain.
+ */
+size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim);
+int gqa_exchange_merge(const float* local_o, const float* local_lse, void* const* peer_bufs,
+                       int32_t rank, int32_t world, uint32_t epoch, int64_t rows,
+                       int32_t head_dim, void* out, int32_t out_dtype, float* out_f32,
+                       float* out_lse, int32_t* status, void* stream);
+
 /* One-wave split heuristic of the reference, gqa_decode/gqa_decode.py:80-102.
  * Returns the split count (>= 1) or a negative error. */
 int gqa_select_num_splits(int32_t num_kv_heads, int32_t seq_len, int32_t block_seq,
