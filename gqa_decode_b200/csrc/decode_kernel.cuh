@@ -301,13 +301,55 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
   const int G = prm.group;
   constexpr int D4 = D / 4;
   const float* lse_g = prm.part_lse + (size_t)first_slot * G;  // [n, G], contiguous slots
-  const bool staged = n * G <= lse_cap;
+  // few partials: every thread fetches the handful of LSEs it needs together with the
+  // outputs (one round trip); many partials: stage the LSEs in shared memory first
+  const bool staged = n > 8 && n * G <= lse_cap;
   if (staged) {
     for (int i = tid; i < n * G; i += nthreads) lse_smem[i] = ld_cg_f32(lse_g + i);
     bar_sync(1, nthreads);
   }
   for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
+    const float4* o_g = reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
+    constexpr int kBatch = 8;
+    if (n <= kBatch) {
+      float4 o[kBatch];
+      float l[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (u < n) {
+          l[u] = ld_cg_f32(lse_g + (size_t)u * G + row);
+          o[u] = ld_cg_f32x4(o_g + (size_t)u * G * D4);
+        } else {
+          l[u] = -INFINITY;
+          o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) mx = fmaxf(mx, l[u]);
+      const float ms = (mx == -INFINITY) ? 0.f : mx;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float wsum = 0.f;
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const float w = fast_exp2((l[u] - ms) * kLog2e);
+        acc.x += w * o[u].x;
+        acc.y += w * o[u].y;
+        acc.z += w * o[u].z;
+        acc.w += w * o[u].w;
+        wsum += w;
+      }
+      const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+      acc.x *= inv;
+      acc.y *= inv;
+      acc.z *= inv;
+      acc.w *= inv;
+      store_final<Q, D>(prm, out_row0 + row, d4, acc);
+      if (d4 == 0 && prm.out_lse)
+        prm.out_lse[out_row0 + row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
+      continue;
+    }
     float mx = -INFINITY;
     if (staged) {
       for (int p = 0; p < n; ++p) mx = fmaxf(mx, lse_smem[p * G + row]);
@@ -317,8 +359,6 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
     const float ms = (mx == -INFINITY) ? 0.f : mx;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    const float4* o_g = reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
-    constexpr int kBatch = 8;
     for (int p0 = 0; p0 < n; p0 += kBatch) {
       float4 o[kBatch];
       float w[kBatch];
@@ -395,8 +435,8 @@ struct Producer {
       return;
     }
     if (lane == 0) {
-      // The descriptor ring is much deeper than the stage ring: a consumer group that
-      // does not own this tile reads the descriptor without waiting for the tile's data.
+      // The descriptor ring is much deeper than the stage ring and is published before the
+      // loads are issued: consumers read it (and fetch a new segment's queries) early.
       sm_desc[it % kDescRing] = d;
       __threadfence_block();
       *sm_published = (int)(it + 1);
@@ -527,8 +567,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   constexpr bool UPPER = Tr::UPPER;
   constexpr int kConsumerWarps = Tr::kWarps;
   constexpr int kConsumerThreads = kConsumerWarps * 32;
-  constexpr int kGroups = Tr::kGroups;
-  constexpr int kWarpsPerGroup = kConsumerWarps / kGroups;
+  static_assert(Tr::kGroups == 1, "every consumer warp takes its slice of every tile");
+  constexpr int kWarpsPerGroup = kConsumerWarps;
   constexpr int kRowsPerWarp = TILE / kWarpsPerGroup;
   static_assert(kRowsPerWarp % 16 == 0, "each consumer warp works in 16-key blocks");
   constexpr int NB = kRowsPerWarp / 16;
@@ -712,13 +752,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   for (uint32_t it = 0;; ++it) {
     const uint32_t s = it % nst, ph = (it / nst) & 1u;
-    // With several consumer groups a tile (and its stage barriers) belongs to one group;
-    // the other groups only need its descriptor, which they take once it is published.
-    const bool mine = kGroups == 1 || (int)(it % kGroups) == warp / kWarpsPerGroup;
+    // The descriptor is published before the tile's loads are even issued, so it is read
+    // first: a new segment's query rows are then fetched while the tile is still in flight.
     bool ok = true;
-    if (mine) {
-      ok = mbar_wait(full0 + 8 * s, ph);
-    } else {
+    if (*sm_published <= (int)it) {
       const unsigned long long t0 = global_timer_ns();
       while (*sm_published <= (int)it) {
         if (global_timer_ns() - t0 > kWaitLimitNs) {
@@ -726,16 +763,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           break;
         }
       }
-      __threadfence_block();
     }
+    __threadfence_block();
+    const TileDesc d = sm_desc[it % kDescRing];
     if (!ok) {
-      // the producer stopped: every consumer warp runs into this within the same tile or two
+      // the producer stopped: every consumer warp runs into this at the same descriptor
       if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
       break;
     }
-    const TileDesc d = sm_desc[it % kDescRing];
     if (d.flags & kTileEnd) break;
-    if (prm.timestamps && tid == 0 && it == 0) prm.timestamps[3 * blockIdx.x + 1] = global_timer_ns();
     const long long g = (long long)d.b * Hkv + d.h;
     const long long out_row0 = (long long)d.b * Hq + (long long)d.h * G;
     if (d.flags & kTileFirst) {
@@ -746,9 +782,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       st.reset();
       seg_tiles = 0;
     }
+    if (!mbar_wait(full0 + 8 * s, ph)) {
+      // every consumer warp waits on the same barrier, so all of them give up together
+      if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
+      break;
+    }
+    if (prm.timestamps && tid == 0 && it == 0) prm.timestamps[3 * blockIdx.x + 1] = global_timer_ns();
     if (d.valid > 0) {
       ++seg_tiles;
-      if (mine) {
+      {
         const uint32_t kb = stage_addr0 + s * Tr::kStageBytes;
         const uint32_t vb = kb + Tr::kBoxesPerTensor * Tr::kBoxBytes;
         const int key0 = (warp % kWarpsPerGroup) * kRowsPerWarp;
@@ -760,7 +802,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
     }
     __syncwarp();
-    if (mine && lane == 0) mbar_arrive(empty0 + 8 * s);
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);
     if (!(d.flags & kTileLast)) continue;
 
     // The next descriptor (normally published long ago) starts a new segment: pull its
@@ -868,15 +910,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     if (!direct && prm.fused_merge) {
       // publish the partial, then draw a ticket: tiles covered (stealing schedule) or one
-      // per partial (static schedules); whoever completes the group merges it
-      __threadfence();
+      // per partial (static schedules); whoever completes the group merges it.  The CTA
+      // barrier orders all threads' partial stores before thread 0's release-acquire
+      // ticket, and the barrier after it hands the acquired view to the other threads.
       bar_sync(1, kConsumerThreads);
       if (tid == 0) {
         const int add = dynamic ? seg_tiles : 1, want = dynamic ? d.ntg : d.n_parts;
-        const int before = atomicAdd(prm.tickets + g, add);
+        const int before = atom_add_acq_rel(prm.tickets + g, add);
         int n = 0;
         if (before + add == want) {
-          __threadfence();
           n = dynamic ? atomicAdd(prm.alloc + g, 0) : d.n_parts;
           if (n < 0 || d.first_slot + n > prm.num_slots) {
             atomicOr(prm.status, kStatusSlotRange);
@@ -890,7 +932,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       bar_sync(1, kConsumerThreads);
       const int n = *sm_flag;
       if (n > 0) {
-        __threadfence();
         merge_group<Q, D>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads, sm_o,
                           kConsumerWarps * grows * kMoStride);
       }

@@ -141,10 +141,9 @@ struct KvFp8Traits {
   static constexpr int D = 128;
   static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
-  static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition
-  static constexpr int kGroups = TILE_ == 128 ? 2 : 1;  // 128-key tiles: two groups of four warps
-                                         // take alternate tiles; either way a warp owns 32 keys of
-                                         // a tile (two independent 16-key blocks)
+  static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition; with 256-key
+                                         // tiles each owns 32 keys (two independent 16-key blocks)
+  static constexpr int kGroups = 1;
   static constexpr int kMoStride = 128 + 4;  // floats per merge row
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;

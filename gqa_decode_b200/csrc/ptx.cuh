@@ -149,6 +149,15 @@ __device__ __forceinline__ float fast_log2(float x) {
   return y;
 }
 
+// Ticket draw with release+acquire semantics at GPU scope: everything this CTA wrote
+// before the preceding CTA barrier is visible to whoever observes the new count, and
+// everything earlier contributors published is visible to this CTA after it.
+__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 __device__ __forceinline__ float ld_cg_f32(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ float4 ld_cg_f32x4(const float4* p) { return __ldcg(p); }
 
