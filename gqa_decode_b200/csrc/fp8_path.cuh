@@ -41,28 +41,51 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
   return r;
 }
-// Two E4M3 codes (low byte first) -> two dequantised, rounded 16-bit values packed
-// for the MMA (low half = first code).
+// Four E4M3 codes in one 32-bit word (lowest byte first) -> two registers of two
+// dequantised, rounded 16-bit values each (b0 = codes 0,1; b1 = codes 2,3).  Written as one
+// PTX block on 16-bit sub-registers so that no separate shift / mask instructions are
+// needed to split words and half2 pairs; the multiply is one packed fp32x2 operation
+// (round-to-nearest per lane, the same result as two fmul.rn).
 template <typename T16>
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t two_codes, float scale) {
-  uint32_t h2;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)two_codes));
-  const float f0 = __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
-  const float f1 = __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
-  // one packed fp32x2 multiply (round-to-nearest per lane, same result as two fmul.rn)
-  unsigned long long in, sc, prod;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(in) : "f"(f0), "f"(f1));
+__device__ __forceinline__ void dequant_word(uint32_t w, float scale, uint32_t& b0, uint32_t& b1) {
+  float f0, f1, f2, f3;
+  asm("{\n\t"
+      ".reg .b16 lo, hi, a, b, c, d;\n\t"
+      ".reg .b32 h0, h1;\n\t"
+      "mov.b32 {lo, hi}, %4;\n\t"
+      "cvt.rn.f16x2.e4m3x2 h0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 h1, hi;\n\t"
+      "mov.b32 {a, b}, h0;\n\t"
+      "mov.b32 {c, d}, h1;\n\t"
+      "cvt.f32.f16 %0, a;\n\t"
+      "cvt.f32.f16 %1, b;\n\t"
+      "cvt.f32.f16 %2, c;\n\t"
+      "cvt.f32.f16 %3, d;\n\t"
+      "}"
+      : "=f"(f0), "=f"(f1), "=f"(f2), "=f"(f3)
+      : "r"(w));
+  unsigned long long in0, in1, sc, p0, p1;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(in0) : "f"(f0), "f"(f1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(in1) : "f"(f2), "f"(f3));
   asm("mov.b64 %0, {%1, %1};" : "=l"(sc) : "f"(scale));
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(in), "l"(sc));
-  float p0, p1;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(prod));
-  return Mma16<T16>::pack(p0, p1);
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p0) : "l"(in0), "l"(sc));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p1) : "l"(in1), "l"(sc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(f0), "=f"(f1) : "l"(p0));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(f2), "=f"(f3) : "l"(p1));
+  b0 = Mma16<T16>::pack(f0, f1);
+  b1 = Mma16<T16>::pack(f2, f3);
 }
 
-__device__ __forceinline__ uint32_t codes_to_f16x2(uint32_t two_codes) {
-  uint32_t h2;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)two_codes));
-  return h2;
+// Four E4M3 codes in one word -> two f16x2 registers holding the codes' exact values.
+__device__ __forceinline__ void codes_word_to_f16x2(uint32_t w, uint32_t& h0, uint32_t& h1) {
+  asm("{\n\t"
+      ".reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t"
+      "}"
+      : "=r"(h0), "=r"(h1)
+      : "r"(w));
 }
 
 // EXACT_V = true : V is dequantised like K (oracle rounding) and P V runs in the query type.
@@ -94,8 +117,8 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int ks = 4 * i + u;
-        const uint32_t b0 = dequant_pair<T16>(ww[u] & 0xffffu, k_scale);
-        const uint32_t b1 = dequant_pair<T16>(ww[u] >> 16, k_scale);
+        uint32_t b0, b1;
+        dequant_word<T16>(ww[u], k_scale, b0, b1);
         Mma16<T16>::run(s[t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
       }
     }
@@ -115,20 +138,24 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
         w[i] = lds32(addr);
         if (PARTIAL && kk >= valid) w[i] = 0u;
       }
-      const uint32_t p01a = prmt(w[0], w[1], 0x5140u), p01b = prmt(w[0], w[1], 0x7362u);
-      const uint32_t p23a = prmt(w[2], w[3], 0x5140u), p23b = prmt(w[2], w[3], 0x7362u);
-      const uint32_t lo[4] = {p01a & 0xffffu, p01a >> 16, p01b & 0xffffu, p01b >> 16};
-      const uint32_t hi[4] = {p23a & 0xffffu, p23a >> 16, p23b & 0xffffu, p23b >> 16};
+      // transpose the 4 keys x 4 columns byte block: word u' of lo2/hi2 holds column pairs
+      // as {key 2c, key 2c+1} (lo2) and {key 2c+8, key 2c+9} (hi2)
+      const uint32_t lo2[2] = {prmt(w[0], w[1], 0x5140u), prmt(w[0], w[1], 0x7362u)};
+      const uint32_t hi2[2] = {prmt(w[2], w[3], 0x5140u), prmt(w[2], w[3], 0x7362u)};
+      uint32_t vb0[4], vb1[4];
+#pragma unroll
+      for (int u2 = 0; u2 < 2; ++u2) {
+        if (EXACT_V) {
+          dequant_word<T16>(lo2[u2], v_scale, vb0[2 * u2], vb0[2 * u2 + 1]);
+          dequant_word<T16>(hi2[u2], v_scale, vb1[2 * u2], vb1[2 * u2 + 1]);
+        } else {
+          codes_word_to_f16x2(lo2[u2], vb0[2 * u2], vb0[2 * u2 + 1]);
+          codes_word_to_f16x2(hi2[u2], vb1[2 * u2], vb1[2 * u2 + 1]);
+        }
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        uint32_t b0, b1;
-        if (EXACT_V) {
-          b0 = dequant_pair<T16>(lo[u], v_scale);
-          b1 = dequant_pair<T16>(hi[u], v_scale);
-        } else {
-          b0 = codes_to_f16x2(lo[u]);
-          b1 = codes_to_f16x2(hi[u]);
-        }
+        const uint32_t b0 = vb0[u], b1 = vb1[u];
         Mma16<TP>::run(st.o[4 * q + u], pa[b][0], pa[b][1], pa[b][2], pa[b][3], b0, b1);
       }
     }
