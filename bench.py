@@ -41,8 +41,8 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 # dram bytes moved per algorithmic byte, from the ncu capture summarised in
-# profiles/decode_kernel_bf16_ragged.md (None until measured)
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": 1.015, "e4m3": None}
+# profiles/decode_kernel_bf16_ragged.md and profiles/decode_kernel_fp8_batch8.md
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": 1.017, "e4m3": 1.011}
 FALLBACK_HBM_GBS = 6650.0
 
 
