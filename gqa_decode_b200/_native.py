@@ -63,6 +63,8 @@ SIGNATURES = {
         ctypes.c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p,
          c_void_p]),
+    "gqa_quantize_kv_fp8": (
+        ctypes.c_int, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gqa_exchange_buffer_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "gqa_exchange_merge": (
         ctypes.c_int,

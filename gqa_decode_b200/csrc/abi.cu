@@ -11,6 +11,7 @@
 #include "decode_kernel.cuh"
 #include "fp8_path.cuh"
 #include "exchange.cuh"
+#include "quantize.cuh"
 
 namespace gqa {
 
@@ -584,6 +585,36 @@ int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num
     merge_rows_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
         o_parts, lse_parts, num_parts, rows, head_dim, static_cast<__nv_bfloat16*>(out), out_f32,
         out_lse);
+  return (int)cudaGetLastError();
+}
+
+int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64_t elems_per_head,
+                        uint8_t* codes, float* scales, float* amax_scratch, void* stream) {
+  if (!x || !codes || !scales || !amax_scratch || num_heads <= 0 || elems_per_head <= 0 ||
+      elems_per_head % 8 || num_heads > 65535)
+    return GQA_ERR_ARG;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7)) return GQA_ERR_ARG;
+  if (x_dtype != GQA_DTYPE_BF16 && x_dtype != GQA_DTYPE_FP16) return GQA_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(amax_scratch, 0, (size_t)num_heads * sizeof(float), st);
+  if (e != cudaSuccess) return (int)e;
+  // enough blocks per head to fill the GPU a few times over, at least 16 KB of input each
+  long long per = elems_per_head / 8 / kQuantThreads / 4;
+  const long long want = (long long)sm_count_or(148) * 8 / num_heads + 1;
+  if (per > want) per = want;
+  if (per < 1) per = 1;
+  const dim3 grid((unsigned)per, (unsigned)num_heads);
+  if (x_dtype == GQA_DTYPE_BF16) {
+    amax_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), elems_per_head, amax_scratch);
+    quantize_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), elems_per_head, amax_scratch, codes, scales);
+  } else {
+    amax_kernel<__half><<<grid, kQuantThreads, 0, st>>>(static_cast<const __half*>(x),
+                                                        elems_per_head, amax_scratch);
+    quantize_kernel<__half><<<grid, kQuantThreads, 0, st>>>(
+        static_cast<const __half*>(x), elems_per_head, amax_scratch, codes, scales);
+  }
   return (int)cudaGetLastError();
 }
 

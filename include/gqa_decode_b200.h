@@ -174,6 +174,17 @@ int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num
                        float* out_f32, float* out_lse, void* stream);
 
 /*
+ * Per-KV-head E4M3 quantisation on the GPU.  Replaces the tensor-op passes of
+ * quantize_kv_fp8, gqa_decode/fp8_utils.py:8-43, for one cache tensor (call it for K and for
+ * V): x [num_heads, elems_per_head] bf16/fp16 (a head's [S, D] slab flattened,
+ * elems_per_head % 8 == 0), codes same shape uint8 (E4M3 bit patterns), scales [num_heads]
+ * fp32 (multiply to dequantise), amax_scratch [num_heads] fp32 (overwritten).  Bit-identical
+ * to the reference arithmetic.
+ */
+int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64_t elems_per_head,
+                        uint8_t* codes, float* scales, float* amax_scratch, void* stream);
+
+/*
  * Sequence-shard exchange over NVLink, fused with the merge (no counterpart in the
  * reference, which is single-GPU): every rank calls this once per decode step after its
  * local kernel wrote (local_o [rows, head_dim] fp32, local_lse [rows]).  peer_bufs is a

@@ -334,3 +334,56 @@ def test_work_stealing_matches_static_schedule(G):
         O.attend_one_sequence(q[i].cpu(), k[i, :, :l].cpu(), v[i, :, :l].cpu()) if l
         else torch.zeros(32, 128, dtype=torch.bfloat16) for i, l in enumerate(lens)])
     _check(G, c, ref)
+
+
+def test_many_short_sequences_and_empty_batch(G):
+    """Hundreds of short sequences (many zero-length, many shorter than a tile) exercise the
+    producer's warp-cooperative scan across several 32-sequence blocks; an all-empty batch
+    must return zeros without touching K/V."""
+    g = torch.Generator().manual_seed(12)
+    b, hq, hkv, d, smax = 300, 16, 4, 128, 200
+    lens = torch.randint(0, smax + 1, (b,), generator=g)
+    lens[::7] = 0
+    lens[5] = smax
+    q = O.randn_bf16((b, hq, d), g)
+    k = O.randn_bf16((b, hkv, smax, d), g)
+    v = O.randn_bf16((b, hkv, smax, d), g)
+    out, lse = G.gqa_decode_attention_batched(q.to(DEV), k.to(DEV), v.to(DEV), lens.to(torch.int32).to(DEV),
+                                              return_lse=True)
+    ref = torch.stack([
+        O.attend_one_sequence(q[i], k[i, :, :l], v[i, :, :l]) if l else torch.zeros(hq, d, dtype=torch.bfloat16)
+        for i, l in enumerate(lens.tolist())])
+    _check(G, out, ref)
+    assert torch.isinf(lse.cpu()[lens == 0]).all()
+    # packed layout of the same batch
+    kp = torch.cat([k[i, :, :l].reshape(-1, d) for i, l in enumerate(lens.tolist())])
+    vp = torch.cat([v[i, :, :l].reshape(-1, d) for i, l in enumerate(lens.tolist())])
+    outp = G.gqa_decode_attention_batched(q.to(DEV), kp.to(DEV), vp.to(DEV), lens.to(torch.int32).to(DEV),
+                                          layout="packed", max_seq_len=smax, num_kv_heads=hkv)
+    assert torch.equal(outp, out)
+    zero = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out0 = G.gqa_decode_attention_batched(q[:4].to(DEV), k[:4].to(DEV), v[:4].to(DEV), zero)
+    assert G.read_status() == 0 and (out0 == 0).all()
+
+
+def test_gpu_quantise_is_bit_identical_to_reference_arithmetic(G):
+    """gqa_quantize_kv_fp8 (two CUDA kernels) against the oracle's tensor-op quantisation:
+    codes and scales must match bit for bit, including outliers, zeros and an all-zero head."""
+    from gqa_decode_b200 import fp8_utils
+
+    g = torch.Generator().manual_seed(3)
+    for dt in (torch.bfloat16, torch.float16):
+        k = O.outlier_kv((8, 777, 128), g, rate=1e-2).to(dt)
+        v = O.outlier_kv((8, 777, 128), g, rate=1e-2).to(dt)
+        v[3] = 0
+        k[0, 5, 7] = 0
+        k8, v8, ks, vs = fp8_utils.quantize_kv_fp8(k.to(DEV), v.to(DEV))
+        r8k, r8v, rks, rvs = O.quantize_kv_e4m3(k, v)
+        assert torch.equal(k8.cpu().view(torch.uint8), r8k.view(torch.uint8))
+        assert torch.equal(v8.cpu().view(torch.uint8), r8v.view(torch.uint8))
+        assert torch.equal(ks.cpu(), rks) and torch.equal(vs.cpu(), rvs)
+    z = load("fp8.npz")
+    k8, v8, ks, vs = fp8_utils.quantize_kv_fp8(from_bits(z["k"], torch.bfloat16).to(DEV),
+                                               from_bits(z["v"], torch.bfloat16).to(DEV))
+    assert np.array_equal(k8.cpu().view(torch.uint8).numpy(), z["k8"])
+    assert np.array_equal(ks.cpu().numpy(), z["k_scale"]) and np.array_equal(vs.cpu().numpy(), z["v_scale"])
