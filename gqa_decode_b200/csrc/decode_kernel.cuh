@@ -242,6 +242,9 @@ struct Kv16Traits {
   static constexpr int kStageBytes = 2 * kBoxesPerTensor * kBoxBytes;
   static constexpr int kBoxCols = 64;                          // elements per box row
   static constexpr int kMoStride = D + 8;  // floats per merge row; +8 keeps float2 stores conflict-free
+  // partials merged per L2 round trip (24 would save 2 us on single-sequence launches but
+  // costs the streaming loop 1.5 % through register pressure)
+  static constexpr int kMergeBatch = 8;
   struct Extra {};
   __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, int, int) {}
   __device__ static __forceinline__ float out_scale(const Extra&) { return 1.f; }
@@ -291,10 +294,11 @@ __device__ __forceinline__ void store_final(const DecodeParams& prm, long long o
 }
 
 // `lse_smem` (capacity `lse_cap` floats) stages the group's n*G log-sum-exps so that the
-// weights come from shared memory; partial outputs are fetched eight at a time so that
-// the L2 round trips overlap instead of forming one dependent chain per partial.
+// weights come from shared memory; partial outputs are fetched kBatch at a time so that
+// the L2 round trips overlap instead of forming one dependent chain per partial (up to
+// kBatch partials need a single round trip).
 // All `nthreads` threads of named barrier 1 must call it together.
-template <typename Q, int D>
+template <typename Q, int D, int kBatch = 8>
 __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_slot, int n,
                                             long long out_row0, int tid, int nthreads,
                                             float* lse_smem, int lse_cap) {
@@ -303,7 +307,7 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
   const float* lse_g = prm.part_lse + (size_t)first_slot * G;  // [n, G], contiguous slots
   // few partials: every thread fetches the handful of LSEs it needs together with the
   // outputs (one round trip); many partials: stage the LSEs in shared memory first
-  const bool staged = n > 8 && n * G <= lse_cap;
+  const bool staged = n > kBatch && n * G <= lse_cap;
   if (staged) {
     for (int i = tid; i < n * G; i += nthreads) lse_smem[i] = ld_cg_f32(lse_g + i);
     bar_sync(1, nthreads);
@@ -311,7 +315,6 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
   for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
     const float4* o_g = reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
-    constexpr int kBatch = 8;
     if (n <= kBatch) {
       float4 o[kBatch];
       float l[kBatch];
@@ -932,8 +935,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       bar_sync(1, kConsumerThreads);
       const int n = *sm_flag;
       if (n > 0) {
-        merge_group<Q, D>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads, sm_o,
-                          kConsumerWarps * grows * kMoStride);
+        merge_group<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads,
+                                           sm_o, kConsumerWarps * grows * kMoStride);
       }
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
@@ -942,11 +945,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   if (tid == 0) {
     if (prm.timestamps) prm.timestamps[3 * blockIdx.x + 2] = global_timer_ns();
-    // the last CTA to finish leaves the chunk deques clean for the next launch
-    __threadfence();
-    if (atomicAdd(prm.done_ctas, 1) == (int)gridDim.x - 1) {
-      for (int i = 0; i < prm.sched.num_ctas; ++i) prm.deques[i] = 0ull;
-      *prm.done_ctas = 0;
+    // work stealing only: the last CTA to finish leaves the chunk deques clean for the
+    // next launch
+    if (dynamic) {
+      __threadfence();
+      if (atomicAdd(prm.done_ctas, 1) == (int)gridDim.x - 1) {
+        for (int i = 0; i < prm.sched.num_ctas; ++i) prm.deques[i] = 0ull;
+        *prm.done_ctas = 0;
+      }
     }
   }
 }

@@ -172,6 +172,7 @@ struct KvFp8Traits {
                                          // tiles each owns 32 keys (two independent 16-key blocks)
   static constexpr int kGroups = 1;
   static constexpr int kMoStride = 128 + 4;  // floats per merge row
+  static constexpr int kMergeBatch = 8;      // partials merged per L2 round trip
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
   static constexpr int kBoxBytes = TILE * 128;
