@@ -12,7 +12,7 @@ from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_voi
 from . import build as _build
 
 DTYPE_BF16, DTYPE_FP16, DTYPE_E4M3 = 0, 1, 2
-LAYOUT_PADDED, LAYOUT_PACKED = 0, 1
+LAYOUT_PADDED, LAYOUT_PACKED, LAYOUT_PAGED_HND, LAYOUT_PAGED_NHD = 0, 1, 2, 3
 FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
 FLAG_FP8_EXACT_V = 4
@@ -41,6 +41,7 @@ class DecodeArgs(ctypes.Structure):
         ("num_splits", c_int32), ("num_ctas", c_int32), ("flags", c_int32),
         ("softmax_scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("stream", c_void_p),
+        ("block_table", c_void_p), ("page_size", c_int32), ("block_table_stride", c_int32),
     ]
 
 

@@ -87,7 +87,9 @@ static EncodeTiledFn encode_fn() {
 
 // View K (or V) as a row-major matrix [total_rows, row_bytes] and describe boxes of
 // [tile_rows x 128 bytes] with the 128-byte swizzle.  Rows past total_rows read as zero.
-static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, int head_dim,
+// `row_elems` is the distance between consecutive rows in elements (head_dim, or
+// Hkv * head_dim when the heads of a page row are interleaved).
+static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long long row_elems,
                        long long total_rows, int tile_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return GQA_ERR_DRIVER;
@@ -96,8 +98,8 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, int head
   CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                : (kv_dtype == GQA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)total_rows};
-  cuuint64_t strides[1] = {(cuuint64_t)head_dim * esz};
+  cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)total_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_elems * esz};
   cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)tile_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -213,8 +215,16 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const int D = a->head_dim;
   const int tile = tile_rows_for(D, a->kv_dtype);
   if (!tile) return GQA_ERR_SHAPE;
-  if (a->kv_layout != GQA_LAYOUT_PADDED && a->kv_layout != GQA_LAYOUT_PACKED) return GQA_ERR_ARG;
+  if (a->kv_layout < GQA_LAYOUT_PADDED || a->kv_layout > GQA_LAYOUT_PAGED_NHD) return GQA_ERR_ARG;
   if (a->kv_layout == GQA_LAYOUT_PACKED && !a->seq_lens) return GQA_ERR_ARG;
+  const bool paged = a->kv_layout >= GQA_LAYOUT_PAGED_HND;
+  if (paged) {
+    if (!a->block_table || a->page_size < 16 || a->page_size % 16 || a->block_table_stride <= 0)
+      return GQA_ERR_ARG;
+    if (a->page_size % tile && tile % a->page_size) return GQA_ERR_SHAPE;
+    if ((long long)a->block_table_stride * a->page_size < a->max_seq_len) return GQA_ERR_ARG;
+    if (a->total_rows % ((long long)a->num_kv_heads * a->page_size)) return GQA_ERR_ARG;
+  }
   if (a->total_rows >= (1ll << 31)) return GQA_ERR_LIMIT;  // TMA coordinates are 32-bit
   const long long groups = (long long)a->batch * a->num_kv_heads;
   if (a->kv_layout == GQA_LAYOUT_PADDED && groups * a->max_seq_len > a->total_rows)
@@ -248,9 +258,14 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   }
 
   CUtensorMap tk, tv;
-  int r = make_kv_map(&tk, a->k, a->kv_dtype, D, a->total_rows, tile);
+  const int box_rows = paged && a->page_size < tile ? a->page_size : tile;
+  // [rows, D] for every layout except page rows with interleaved heads: [pages * page_size, Hkv * D]
+  const bool nhd = a->kv_layout == GQA_LAYOUT_PAGED_NHD;
+  const long long row_elems = nhd ? (long long)a->num_kv_heads * D : D;
+  const long long map_rows = nhd ? a->total_rows / a->num_kv_heads : a->total_rows;
+  int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows);
   if (r) return r;
-  r = make_kv_map(&tv, a->v, a->kv_dtype, D, a->total_rows, tile);
+  r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows);
   if (r) return r;
 
   char* ws = static_cast<char*>(a->workspace);
@@ -290,6 +305,15 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   prm.no_merge = no_merge ? 1 : 0;
   prm.num_slots = (int)w.slots;
   prm.timestamps = g_timestamp_buffer.load(std::memory_order_relaxed);
+  prm.block_table = paged ? a->block_table : nullptr;
+  prm.page_size = paged ? a->page_size : 0;
+  prm.table_stride = paged ? a->block_table_stride : 0;
+  prm.box_rows = box_rows;
+  prm.box_shift = 0;
+  while ((1 << prm.box_shift) < box_rows) ++prm.box_shift;
+  prm.page_shift = -1;
+  if (paged && (a->page_size & (a->page_size - 1)) == 0)
+    for (prm.page_shift = 0; (1 << prm.page_shift) < a->page_size;) ++prm.page_shift;
 
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   if (workspace_needs_clear(a->workspace, w.lse_off)) {

@@ -64,6 +64,13 @@ struct DecodeParams {
   int num_stages;
   int num_slots;        // partial slots the workspace holds
   unsigned long long* timestamps;  // optional diagnostics: per CTA {start, first tile landed, end} in ns
+  // paged K/V (sched.layout >= kLayoutPagedHnd)
+  const int* block_table;   // [batch, table_stride] page numbers
+  int page_size;            // rows per page
+  int table_stride;         // table entries per sequence
+  int box_rows;             // rows per TMA box: min(tile, page_size), a power of two
+  int box_shift;            // log2(box_rows)
+  int page_shift;           // log2(page_size), or -1 when page_size is not a power of two
 };
 
 // What the producer tells the consumers about the tile in a pipeline stage.
@@ -411,6 +418,15 @@ struct BlockShape {
   static constexpr bool kRebalanceRegs = Tr::kWarps == 8;
 };
 
+// Stage index and use parity of the next tile (it % nst and (it / nst) & 1 without the
+// divisions: both run once per tile on every warp's critical path).
+__device__ __forceinline__ void next_stage(uint32_t& stage, uint32_t& parity, int nst) {
+  if (++stage == (uint32_t)nst) {
+    stage = 0;
+    parity ^= 1u;
+  }
+}
+
 // ------------------------------------------------------------------ producer
 template <class Tr>
 struct Producer {
@@ -421,15 +437,22 @@ struct Producer {
   volatile int* sm_published;
   uint32_t full0, empty0, stage_addr0;
   uint64_t policy;
-  uint32_t it;
+  uint32_t it;        // tiles posted so far
+  uint32_t stg, par;  // stage of tile `it` and the parity of its use: it % nst, (it / nst) & 1
   int nst, lane;
   bool dead;
+  // paged layouts: 32 consecutive block-table entries of one sequence, one per lane
+  int pg_seq, pg_base, pg_entry;
 
+  __device__ __forceinline__ void step() {
+    ++it;
+    next_stage(stg, par, nst);
+  }
   // Wait for the stage of tile `it` to be free, publish its descriptor and start the
   // loads (or just signal when there is no data).  All lanes call it; lane 0 acts.
   __device__ __forceinline__ void post(const TileDesc& d, long long row) {
     if (dead) return;
-    const uint32_t s = it % nst, ph = (it / nst) & 1u;
+    const uint32_t s = stg, ph = par;
     int ok = 1;
     if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
     if (!__shfl_sync(0xffffffffu, ok, 0)) {
@@ -459,7 +482,64 @@ struct Producer {
       }
     }
     __syncwarp();
-    ++it;
+    step();
+  }
+
+  // Paged layouts: the tile holds keys [key0, key0 + d.valid) of sequence d.b, head d.h.
+  // It is fetched as boxes of prm->box_rows rows, each inside one page; lane j resolves and
+  // issues box j, and boxes that start past the last valid key are not fetched (consumers
+  // mask those rows).  The block table is read 32 entries at a time, one per lane.
+  __device__ __forceinline__ void post_paged(const TileDesc& d, int key0) {
+    if (dead) return;
+    const uint32_t s = stg, ph = par;
+    // (shifts instead of divisions: this runs once per tile on the producer's critical path)
+    const int ps = prm->page_size, psh = prm->page_shift, bsh = prm->box_shift;
+    const int nbox = (d.valid + (1 << bsh) - 1) >> bsh;
+    const int last_key = key0 + d.valid - 1;
+    const int pg_first = psh >= 0 ? key0 >> psh : key0 / ps;
+    const int pg_last = psh >= 0 ? last_key >> psh : last_key / ps;
+    if (d.b != pg_seq || pg_first < pg_base || pg_last >= pg_base + 32) {
+      pg_seq = d.b;
+      pg_base = pg_first;
+      const int e = pg_base + lane;
+      pg_entry = e < prm->table_stride
+                     ? __ldg(prm->block_table + (long long)d.b * prm->table_stride + e)
+                     : 0;
+    }
+    const int key = key0 + (lane << bsh);  // first key of this lane's box
+    const int pidx = psh >= 0 ? key >> psh : key / ps;
+    const int page = __shfl_sync(0xffffffffu, pg_entry, min(pidx - pg_base, 31));
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
+    if (!__shfl_sync(0xffffffffu, ok, 0)) {
+      if (lane == 0) atomicOr(prm->status, kStatusWaitEmpty);
+      dead = true;
+      return;
+    }
+    const uint32_t fb = full0 + 8 * s;
+    if (lane == 0) {
+      sm_desc[it % kDescRing] = d;
+      __threadfence_block();
+      *sm_published = (int)(it + 1);
+      mbar_expect_tx(fb, ((uint32_t)nbox << bsh) * 128u * 2u * Tr::kBoxesPerTensor);
+    }
+    __syncwarp();
+    if (lane < nbox) {
+      const int off = key - pidx * ps;
+      const bool hnd = prm->sched.layout == kLayoutPagedHnd;
+      const int row = hnd ? (page * prm->sched.num_kv_heads + d.h) * ps + off : page * ps + off;
+      const int col0 = hnd ? 0 : d.h * (Tr::kBoxCols * Tr::kBoxesPerTensor);
+      const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes + ((uint32_t)lane << (bsh + 7));
+      const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+#pragma unroll
+      for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+        tma_load_2d(kdst + bx * Tr::kBoxBytes, tm_k, fb, col0 + bx * Tr::kBoxCols, row, policy);
+#pragma unroll
+      for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+        tma_load_2d(vdst + bx * Tr::kBoxBytes, tm_v, fb, col0 + bx * Tr::kBoxCols, row, policy);
+    }
+    __syncwarp();
+    step();
   }
 };
 
@@ -628,9 +708,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     pr.stage_addr0 = stage_addr0;
     pr.policy = l2_evict_first_policy();
     pr.it = 0;
+    pr.stg = 0;
+    pr.par = 0;
     pr.nst = nst;
     pr.lane = lane;
     pr.dead = false;
+    pr.pg_seq = -1;
+    pr.pg_base = 0;
+    pr.pg_entry = 0;
+    const bool paged = prm.sched.layout >= kLayoutPagedHnd;
     const int cta = blockIdx.x;
     TileDesc d;
     if (prm.sched.num_splits > 0) {
@@ -657,7 +743,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int t = 0; t < ntiles; ++t) {
           d.valid = min(TILE, rows - t * TILE);
           d.flags = (t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0);
-          pr.post(d, sg.kv_row0 + sg.row_begin + (long long)t * TILE);
+          if (paged) pr.post_paged(d, sg.row_begin + t * TILE);
+          else pr.post(d, sg.kv_row0 + sg.row_begin + (long long)t * TILE);
         }
       }
     } else {
@@ -707,7 +794,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           d.valid = min(TILE, wk.len - wk.ti * TILE);
           d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0);
-          pr.post(d, row0 + (long long)wk.ti * TILE);
+          if (paged) pr.post_paged(d, wk.ti * TILE);
+          else pr.post(d, row0 + (long long)wk.ti * TILE);
           open = !last;
           wk.advance();
         }
@@ -753,8 +841,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   typename Tr::Extra extra;
   int seg_tiles = 0;
 
-  for (uint32_t it = 0;; ++it) {
-    const uint32_t s = it % nst, ph = (it / nst) & 1u;
+  uint32_t s = 0, ph = 0;  // stage of tile `it` and the parity of its use
+  for (uint32_t it = 0;; ++it, next_stage(s, ph, nst)) {
     // The descriptor is published before the tile's loads are even issued, so it is read
     // first: a new segment's query rows are then fetched while the tile is still in flight.
     bool ok = true;

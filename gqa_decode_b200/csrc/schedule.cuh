@@ -49,6 +49,8 @@ GQA_HD long long fast_mod(long long a, long long b) { return a % b; }
 enum KvLayout : int {
   kLayoutPadded = 0,  // K/V [batch, Hkv, max_seq, D]: head slab of (b,h) starts at row (b*Hkv+h)*max_seq
   kLayoutPacked = 1,  // K/V [sum_b Hkv*len_b, D]: sequence b holds [Hkv, len_b, D] after all earlier sequences
+  kLayoutPagedHnd = 2,  // K/V [num_pages, Hkv, page_size, D] + block table (rows resolved by the producer)
+  kLayoutPagedNhd = 3,  // K/V [num_pages, page_size, Hkv, D] + block table
 };
 
 struct SchedParams {
@@ -103,7 +105,7 @@ struct Walker {
       l = p.seq_lens[bb];
 #endif
       if (l < 0) l = 0;
-      if (p.layout == kLayoutPadded && l > p.max_seq) l = p.max_seq;
+      if (p.layout != kLayoutPacked && l > p.max_seq) l = p.max_seq;
     }
     return l;
   }
@@ -156,6 +158,7 @@ struct Walker {
   }
   GQA_HD long long group_index() const { return (long long)b * p.num_kv_heads + h; }
   GQA_HD long long kv_row0() const {
+    if (p.layout >= kLayoutPagedHnd) return 0;  // paged: rows come from the block table
     return p.layout == kLayoutPadded ? group_index() * (long long)p.max_seq
                                      : rows_before_seq * p.num_kv_heads + (long long)h * len;
   }

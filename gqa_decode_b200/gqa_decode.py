@@ -172,6 +172,7 @@ def gqa_decode_attention_batched(
     num_kv_heads: Optional[int] = None,
     fp8_exact_v: bool = False,
     work_stealing: bool = False,
+    block_table: Optional[torch.Tensor] = None,
     _entry: str = "auto",
     _no_merge: bool = False,
     _plan_only: bool = False,
@@ -184,6 +185,12 @@ def gqa_decode_attention_batched(
     layout="packed": k/v ``[Hkv * sum(len), D]`` where sequence ``b`` stores its
       ``[Hkv, len_b, D]`` slab after all earlier sequences; ``seq_lens``, ``num_kv_heads``
       and ``max_seq_len`` (a bound on every length) are required.
+    layout="paged_hnd": k/v ``[num_pages, Hkv, page_size, D]``; layout="paged_nhd": k/v
+      ``[num_pages, page_size, Hkv, D]``.  ``block_table`` int32 ``[B, max_pages]`` on the
+      device names the page of every ``page_size`` consecutive keys of a sequence; entries
+      past a sequence's last page are never read.  ``seq_lens`` is required;
+      ``max_seq_len`` defaults to ``max_pages * page_size``.  ``page_size`` is a multiple of
+      16 that divides the kernel's tile or is a multiple of it (any power of two >= 16 works).
     k/v dtype is q's dtype, or ``float8_e4m3fn`` with ``k_scale``/``v_scale`` fp32
     ``[B, Hkv]`` (per sequence and KV head, the reference's fp8_utils scheme).
     num_splits: ``None`` = balanced persistent schedule; ``K`` = K partials per
@@ -232,8 +239,32 @@ def gqa_decode_attention_batched(
         total_rows, kv_head_dim = k_cache.shape
         smax = int(max_seq_len)
         code_layout = _native.LAYOUT_PACKED
+    elif layout in ("paged_hnd", "paged_nhd"):
+        if k_cache.dim() != 4 or block_table is None or seq_lens is None:
+            raise ValueError(
+                "paged layouts expect k/v=(num_pages, num_kv_heads, page_size, head_dim) or "
+                "(num_pages, page_size, num_kv_heads, head_dim), block_table and seq_lens")
+        if layout == "paged_hnd":
+            num_pages, num_kv_heads, page_size, kv_head_dim = k_cache.shape
+            code_layout = _native.LAYOUT_PAGED_HND
+        else:
+            num_pages, page_size, num_kv_heads, kv_head_dim = k_cache.shape
+            code_layout = _native.LAYOUT_PAGED_NHD
+        if (block_table.dtype != torch.int32 or block_table.device != q.device
+                or block_table.dim() != 2 or block_table.shape[0] != batch):
+            raise ValueError("block_table must be an int32 CUDA tensor of shape [batch, max_pages]")
+        block_table = block_table.contiguous()
+        tile = lib.gqa_decode_tile_rows(
+            head_dim, _native.DTYPE_E4M3 if fp8 else _DTYPE_CODE[q.dtype])
+        if page_size < 16 or page_size % 16 or (tile > 0 and page_size % tile and tile % page_size):
+            raise ValueError(
+                f"page_size must be a multiple of 16 that divides or is a multiple of {tile}")
+        total_rows = num_pages * num_kv_heads * page_size
+        smax = block_table.shape[1] * page_size if max_seq_len is None else int(max_seq_len)
+        if smax > block_table.shape[1] * page_size:
+            raise ValueError("max_seq_len exceeds what the block table can address")
     else:
-        raise ValueError("layout must be 'padded' or 'packed'")
+        raise ValueError("layout must be 'padded', 'packed', 'paged_hnd' or 'paged_nhd'")
     if kv_head_dim != head_dim:
         raise ValueError("Q/K/V head_dim mismatch")
     if fp8:
@@ -289,6 +320,9 @@ def gqa_decode_attention_batched(
     a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     a.stream = torch.cuda.current_stream(dev).cuda_stream
+    if code_layout >= _native.LAYOUT_PAGED_HND:
+        a.block_table = block_table.data_ptr()
+        a.page_size, a.block_table_stride = page_size, block_table.shape[1]
     if fp8:
         fn = lib.gqa_decode_attention_fp8
     elif _entry == "persistent":
@@ -298,7 +332,7 @@ def gqa_decode_attention_batched(
     extras = tuple(t for t in (out_f32, out_lse) if t is not None)
     result = (out, *extras) if extras else out
     if _plan_only:
-        keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse)
+        keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse, block_table)
         return DecodePlan(fn, a, dev, result, keep)
     with torch.cuda.device(dev):
         _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")

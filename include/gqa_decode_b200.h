@@ -30,6 +30,12 @@ extern "C" {
  * exactly like the reference's [Hkv, S, D] tensors, gqa_decode/gqa_decode.py:44) */
 #define GQA_LAYOUT_PADDED 0 /* [batch, Hkv, max_seq_len, D]; batch = 1 is the reference layout */
 #define GQA_LAYOUT_PACKED 1 /* sequence b holds [Hkv, len_b, D], sequences back to back */
+/* Paged caches as serving engines hold them (the reference has only contiguous tensors): key r
+ * of sequence b lives in page block_table[b * block_table_stride + r / page_size], row
+ * r % page_size.  page_size is a multiple of 16 that divides, or is a multiple of, the tile
+ * (gqa_decode_tile_rows()).  Entries of the table past a sequence's last page are ignored. */
+#define GQA_LAYOUT_PAGED_HND 2 /* [num_pages, Hkv, page_size, D] */
+#define GQA_LAYOUT_PAGED_NHD 3 /* [num_pages, page_size, Hkv, D] */
 
 /* flags */
 #define GQA_FLAG_SEPARATE_MERGE 1 /* run the merge as a second kernel instead of in-kernel */
@@ -72,7 +78,8 @@ typedef struct gqa_decode_args {
   int32_t num_kv_heads;
   int32_t head_dim;         /* 64, 128 or 256 (E4M3: 128) */
   int32_t max_seq_len;      /* rows per head slab (padded layout); bound on every length */
-  int64_t total_rows;       /* rows of the whole K (= V) allocation, viewed as [rows, head_dim] */
+  int64_t total_rows;       /* rows of the whole K (= V) allocation, viewed as [rows, head_dim]
+                               (paged: num_pages * num_kv_heads * page_size) */
   int32_t q_dtype;          /* GQA_DTYPE_BF16 | GQA_DTYPE_FP16 */
   int32_t kv_dtype;         /* q_dtype, or GQA_DTYPE_E4M3 */
   int32_t kv_layout;        /* GQA_LAYOUT_* */
@@ -83,6 +90,9 @@ typedef struct gqa_decode_args {
   void* workspace;          /* device scratch of gqa_decode_workspace_bytes(); reusable across calls */
   size_t workspace_bytes;
   void* stream;             /* cudaStream_t */
+  const int32_t* block_table;  /* paged layouts: device [batch, block_table_stride] page numbers */
+  int32_t page_size;           /* paged layouts: rows per page */
+  int32_t block_table_stride;  /* paged layouts: table entries per sequence */
 } gqa_decode_args_t;
 
 /* Bytes of device scratch a launch with these sizes needs (partials, tickets, status). */
