@@ -115,8 +115,13 @@ static int group_overhead_for(int head_dim, int kv_dtype) {
   return (kv_dtype == GQA_DTYPE_E4M3 || head_dim == 256) ? 1 : 2;
 }
 
+#ifndef GQA_FP8_WARPS
+#define GQA_FP8_WARPS 8
+#endif
+constexpr int kFp8Warps = GQA_FP8_WARPS;
+constexpr int kFp8Tile = kFp8Warps == 12 ? 192 : 256;
 static int tile_rows_for(int head_dim, int kv_dtype) {
-  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? 256 : 0;
+  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? kFp8Tile : 0;
   if (head_dim == 256) return 64;
   if (head_dim == 128) return 64;
   if (head_dim == 64) return 128;
@@ -328,18 +333,18 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     const bool exact_v = (a->flags & GQA_FLAG_FP8_EXACT_V) != 0;
     if (exact_v) {
       if (bf) {
-        if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, true, true>);
-        GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, false, true>);
+        if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, kFp8Tile, true, true, kFp8Warps>);
+        GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, kFp8Tile, false, true, kFp8Warps>);
       }
-      if (upper) GQA_LAUNCH(KvFp8Traits<__half, 256, true, true>);
-      GQA_LAUNCH(KvFp8Traits<__half, 256, false, true>);
+      if (upper) GQA_LAUNCH(KvFp8Traits<__half, kFp8Tile, true, true, kFp8Warps>);
+      GQA_LAUNCH(KvFp8Traits<__half, kFp8Tile, false, true, kFp8Warps>);
     }
     if (bf) {
-      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, true, false>);
-      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, 256, false, false>);
+      if (upper) GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, kFp8Tile, true, false, kFp8Warps>);
+      GQA_LAUNCH(KvFp8Traits<__nv_bfloat16, kFp8Tile, false, false, kFp8Warps>);
     }
-    if (upper) GQA_LAUNCH(KvFp8Traits<__half, 256, true, false>);
-    GQA_LAUNCH(KvFp8Traits<__half, 256, false, false>);
+    if (upper) GQA_LAUNCH(KvFp8Traits<__half, kFp8Tile, true, false, kFp8Warps>);
+    GQA_LAUNCH(KvFp8Traits<__half, kFp8Tile, false, false, kFp8Warps>);
   }
   if (D == 256) {
     if (bf) {

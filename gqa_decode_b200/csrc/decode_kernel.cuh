@@ -63,7 +63,10 @@ struct DecodeParams {
   int no_merge;         // 1: every segment is written as a partial and nothing is merged
   int num_stages;
   int num_slots;        // partial slots the workspace holds
-  unsigned long long* timestamps;  // optional diagnostics: per CTA {start, first tile landed, end} in ns
+  unsigned long long* timestamps;  // optional diagnostics: per CTA {start, first tile landed, end} in ns;
+                                   // builds with GQA_PROFILE_WAITS append, after those 3 * grid words,
+                                   // per CTA {producer wait cycles, producer cycles, tiles posted,
+                                   // consumer warp 0 wait-for-data cycles, consumer cycles}
   // paged K/V (sched.layout >= kLayoutPagedHnd)
   const int* block_table;   // [batch, table_stride] page numbers
   int page_size;            // rows per page
@@ -249,6 +252,8 @@ struct Kv16Traits {
   static constexpr int kStageBytes = 2 * kBoxesPerTensor * kBoxBytes;
   static constexpr int kBoxCols = 64;                          // elements per box row
   static constexpr int kMoStride = D + 8;  // floats per merge row; +8 keeps float2 stores conflict-free
+  // float index of (merge row, column) inside a warp's block of merge rows
+  __device__ static __forceinline__ int mo_index(int row, int col) { return row * kMoStride + col; }
   // partials merged per L2 round trip (24 would save 2 us on single-sequence launches but
   // costs the streaming loop 1.5 % through register pressure)
   static constexpr int kMergeBatch = 8;
@@ -413,9 +418,9 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
 // warpgroup and 224 for the consumers.
 template <class Tr>
 struct BlockShape {
-  static constexpr int kProducerWarps = Tr::kWarps == 8 ? 4 : 1;
+  static constexpr int kProducerWarps = Tr::kWarps >= 8 ? 4 : 1;
   static constexpr int kThreads = (Tr::kWarps + kProducerWarps) * 32;
-  static constexpr bool kRebalanceRegs = Tr::kWarps == 8;
+  static constexpr bool kRebalanceRegs = Tr::kWarps >= 8;
 };
 
 // Stage index and use parity of the next tile (it % nst and (it / nst) & 1 without the
@@ -443,6 +448,9 @@ struct Producer {
   bool dead;
   // paged layouts: 32 consecutive block-table entries of one sequence, one per lane
   int pg_seq, pg_base, pg_entry;
+#ifdef GQA_PROFILE_WAITS
+  long long wait_cycles;  // diagnostics build: cycles spent waiting for a free stage
+#endif
 
   __device__ __forceinline__ void step() {
     ++it;
@@ -454,7 +462,13 @@ struct Producer {
     if (dead) return;
     const uint32_t s = stg, ph = par;
     int ok = 1;
+#ifdef GQA_PROFILE_WAITS
+    const long long w0 = clock64();
+#endif
     if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
+#ifdef GQA_PROFILE_WAITS
+    wait_cycles += clock64() - w0;
+#endif
     if (!__shfl_sync(0xffffffffu, ok, 0)) {
       if (lane == 0) atomicOr(prm->status, kStatusWaitEmpty);
       dead = true;
@@ -713,6 +727,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     pr.nst = nst;
     pr.lane = lane;
     pr.dead = false;
+#ifdef GQA_PROFILE_WAITS
+    pr.wait_cycles = 0;
+    const long long pc0 = clock64();
+#endif
     pr.pg_seq = -1;
     pr.pg_base = 0;
     pr.pg_entry = 0;
@@ -812,11 +830,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     d.valid = 0;
     d.flags = kTileEnd;
     pr.post(d, 0);
+#ifdef GQA_PROFILE_WAITS
+    if (prm.timestamps && lane == 0) {
+      unsigned long long* ts = prm.timestamps + 3 * gridDim.x + 5 * blockIdx.x;
+      ts[0] = (unsigned long long)pr.wait_cycles;
+      ts[1] = (unsigned long long)(clock64() - pc0);
+      ts[2] = pr.it;
+    }
+#endif
     return;
   }
 
   // -------------------------------------------------------------- consumers
-  if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+  if constexpr (BlockShape<Tr>::kRebalanceRegs) {
+    // 8 consumer warps: 12 warps x 168 at launch -> 224; 12 consumer warps: 16 x 128 -> 152
+    if constexpr (Tr::kWarps == 12) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+  }
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
   const bool dynamic = prm.sched.num_splits == 0 && prm.sched.steal;
@@ -840,6 +870,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint32_t qa[D / 16][4];
   typename Tr::Extra extra;
   int seg_tiles = 0;
+#ifdef GQA_PROFILE_WAITS
+  long long cons_wait = 0;  // diagnostics build: cycles this warp waited for data
+  const long long cc0 = clock64();
+#endif
 
   uint32_t s = 0, ph = 0;  // stage of tile `it` and the parity of its use
   for (uint32_t it = 0;; ++it, next_stage(s, ph, nst)) {
@@ -873,11 +907,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       st.reset();
       seg_tiles = 0;
     }
+#ifdef GQA_PROFILE_WAITS
+    const long long cw0 = clock64();
+#endif
     if (!mbar_wait(full0 + 8 * s, ph)) {
       // every consumer warp waits on the same barrier, so all of them give up together
       if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
       break;
     }
+#ifdef GQA_PROFILE_WAITS
+    cons_wait += clock64() - cw0;
+#endif
     if (prm.timestamps && tid == 0 && it == 0) prm.timestamps[3 * blockIdx.x + 1] = global_timer_ns();
     if (d.valid > 0) {
       ++seg_tiles;
@@ -948,16 +988,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         L += sm_ml[(w * grows + row) * 2 + 1] * fast_exp2(sm_ml[(w * grows + row) * 2] - Ms);
       const float f = L > 0.f ? fast_exp2(st.m[r] - Ms) / L * Tr::out_scale(extra) : 0.f;
       if (row < G) {
-        float* dst = sm_o + ((size_t)warp * grows + row) * kMoStride;
+        float* dst = sm_o + (size_t)warp * grows * kMoStride;
 #pragma unroll
         for (int nt = 0; nt < D / 8; ++nt) {
-          if constexpr (Tr::kFp8) {
-            dst[Tr::out_col(nt, c, 0)] = st.o[nt][2 * r] * f;
-            dst[Tr::out_col(nt, c, 1)] = st.o[nt][2 * r + 1] * f;
-          } else {
-            *reinterpret_cast<float2*>(dst + Tr::out_col(nt, c, 0)) =
-                make_float2(st.o[nt][2 * r] * f, st.o[nt][2 * r + 1] * f);
-          }
+          *reinterpret_cast<float2*>(dst + Tr::mo_index(row, Tr::out_col(nt, c, 0))) =
+              make_float2(st.o[nt][2 * r] * f, st.o[nt][2 * r + 1] * f);
         }
       }
     }
@@ -969,7 +1004,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) {
         const float4 v = *reinterpret_cast<const float4*>(
-            sm_o + ((size_t)w * grows + row) * kMoStride + 4 * d4);
+            sm_o + (size_t)w * grows * kMoStride + Tr::mo_index(row, 4 * d4));
         acc.x += v.x;
         acc.y += v.y;
         acc.z += v.z;
@@ -1031,6 +1066,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     bar_sync(1, kConsumerThreads);
   }
 
+#ifdef GQA_PROFILE_WAITS
+  if (prm.timestamps && tid == 0) {
+    unsigned long long* ts = prm.timestamps + 3 * gridDim.x + 5 * blockIdx.x;
+    ts[3] = (unsigned long long)cons_wait;
+    ts[4] = (unsigned long long)(clock64() - cc0);
+  }
+#endif
   if (tid == 0) {
     if (prm.timestamps) prm.timestamps[3 * blockIdx.x + 2] = global_timer_ns();
     // work stealing only: the last CTA to finish leaves the chunk deques clean for the

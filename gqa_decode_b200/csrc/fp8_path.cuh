@@ -14,9 +14,9 @@
 //
 // Because the contraction index of an MMA may be permuted freely as long as A and B
 // agree, the d axis is permuted so that a thread's 16-byte shared load feeds four
-// k-steps of Q K^T, and the output columns of P V are permuted so that four
-// consecutive bytes of a V row feed four MMA tiles.  Q fragments and the epilogue
-// use the same permutations.
+// k-steps of Q K^T (the Q fragments use the same permutation).  V is fetched with the
+// byte-transposing ldmatrix (ldmatrix ... .m16n16 ... .trans ... .b8), which delivers four
+// keys of one column per register, ready for two conversions into an MMA B fragment.
 #pragma once
 #include <type_traits>
 
@@ -46,6 +46,16 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // PTX block on 16-bit sub-registers so that no separate shift / mask instructions are
 // needed to split words and half2 pairs; the multiply is one packed fp32x2 operation
 // (round-to-nearest per lane, the same result as two fmul.rn).
+__device__ __forceinline__ void codes_word_to_f16x2_fwd(uint32_t w, uint32_t& h0, uint32_t& h1) {
+  asm("{\n\t"
+      ".reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t"
+      "}"
+      : "=r"(h0), "=r"(h1)
+      : "r"(w));
+}
 template <typename T16>
 __device__ __forceinline__ void dequant_word(uint32_t w, float scale, uint32_t& b0, uint32_t& b1) {
   float f0, f1, f2, f3;
@@ -74,6 +84,34 @@ __device__ __forceinline__ void dequant_word(uint32_t w, float scale, uint32_t& 
   asm("mov.b64 {%0, %1}, %2;" : "=f"(f2), "=f"(f3) : "l"(p1));
   b0 = Mma16<T16>::pack(f0, f1);
   b1 = Mma16<T16>::pack(f2, f3);
+}
+
+// N words at once, written stage by stage (all first conversions, then all widenings, all
+// multiplies, all roundings): long runs of independent instructions keep the slow
+// conversion pipe fed instead of leaving each word's five-deep dependency chain exposed.
+template <typename T16, int N>
+__device__ __forceinline__ void dequant_words(const uint32_t (&w)[N], float scale,
+                                              uint32_t (&b)[2 * N]) {
+  uint32_t h[2 * N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) codes_word_to_f16x2_fwd(w[j], h[2 * j], h[2 * j + 1]);
+  float f[4 * N];
+#pragma unroll
+  for (int j = 0; j < 2 * N; ++j)
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+        : "=f"(f[2 * j]), "=f"(f[2 * j + 1])
+        : "r"(h[j]));
+  unsigned long long sc;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(sc) : "f"(scale));
+#pragma unroll
+  for (int j = 0; j < 2 * N; ++j) {
+    unsigned long long in, pr;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(in) : "f"(f[2 * j]), "f"(f[2 * j + 1]));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(in), "l"(sc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(f[2 * j]), "=f"(f[2 * j + 1]) : "l"(pr));
+  }
+#pragma unroll
+  for (int j = 0; j < 2 * N; ++j) b[j] = Mma16<T16>::pack(f[2 * j], f[2 * j + 1]);
 }
 
 // Four E4M3 codes in one word -> two f16x2 registers holding the codes' exact values.
@@ -107,6 +145,33 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
   float s[2 * NB][4];
 #pragma unroll
   for (int t = 0; t < 2 * NB; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+#ifndef GQA_FP8_KBATCH
+#define GQA_FP8_KBATCH 0
+#endif
+#if GQA_FP8_KBATCH
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int t0 = 0; t0 < 2 * NB; t0 += GQA_FP8_KBATCH) {
+      uint32_t ww[4 * GQA_FP8_KBATCH], bb[8 * GQA_FP8_KBATCH];
+#pragma unroll
+      for (int t = 0; t < GQA_FP8_KBATCH; ++t) {
+        const int key = key0 + 8 * (t0 + t) + n;
+        const uint4 w = lds128(k_base + key * 128 + (((2 * c + i) ^ (key & 7)) << 4));
+        ww[4 * t] = w.x, ww[4 * t + 1] = w.y, ww[4 * t + 2] = w.z, ww[4 * t + 3] = w.w;
+      }
+      dequant_words<T16, 4 * GQA_FP8_KBATCH>(ww, k_scale, bb);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int ks = 4 * i + u;
+#pragma unroll
+        for (int t = 0; t < GQA_FP8_KBATCH; ++t)
+          Mma16<T16>::run(s[t0 + t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], bb[8 * t + 2 * u],
+                          bb[8 * t + 2 * u + 1]);
+      }
+    }
+  }
+#else
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
 #pragma unroll
@@ -123,39 +188,36 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
       }
     }
   }
+#endif
   uint32_t pa[NB][4];
   softmax_block<TP, D, UPPER, PARTIAL, NB>(s, st, pa, scale_log2, key0, valid, lane);
+  // O += P V.  V fragments come from the byte-transposing ldmatrix: the 16 row addresses of
+  // a matrix are given in the order 0,1,8,9, 2,3,10,11, ... so that the four rows a thread
+  // receives in one register (matrix rows 4c..4c+3) are keys 2c, 2c+1, 2c+8, 2c+9 - exactly
+  // the k indices of its B fragment.  Register u of a load covers output columns
+  // 32q + 8u + n: accumulator tile 4q + u, natural column order.
+  const int mr = lane & 15;
+  const int vkey = 2 * (mr >> 2) + (mr & 1) + 8 * ((mr >> 1) & 1);  // key of this lane's matrix row
+  uint32_t live = 0xffffffffu;  // byte mask of the keys that exist (PARTIAL tiles)
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
+  for (int b = 0; b < NB; ++b) {
+    if (PARTIAL) {
+      const int k0 = key0 + 16 * b + 2 * c;
+      live = (k0 < valid ? 0x000000ffu : 0u) | (k0 + 1 < valid ? 0x0000ff00u : 0u) |
+             (k0 + 8 < valid ? 0x00ff0000u : 0u) | (k0 + 9 < valid ? 0xff000000u : 0u);
+    }
+    const int kk = key0 + 16 * b + vkey;
+    const uint32_t row_addr = v_base + kk * 128;
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int q = 0; q < 4; ++q) {
       uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int kk = key0 + 16 * b + 2 * c + (i & 1) + (i >> 1) * 8;
-        const uint32_t addr =
-            v_base + kk * 128 + (((2 * q + (n >> 2)) ^ (kk & 7)) << 4) + 4 * (n & 3);
-        w[i] = lds32(addr);
-        if (PARTIAL && kk >= valid) w[i] = 0u;
-      }
-      // transpose the 4 keys x 4 columns byte block: word u' of lo2/hi2 holds column pairs
-      // as {key 2c, key 2c+1} (lo2) and {key 2c+8, key 2c+9} (hi2)
-      const uint32_t lo2[2] = {prmt(w[0], w[1], 0x5140u), prmt(w[0], w[1], 0x7362u)};
-      const uint32_t hi2[2] = {prmt(w[2], w[3], 0x5140u), prmt(w[2], w[3], 0x7362u)};
-      uint32_t vb0[4], vb1[4];
-#pragma unroll
-      for (int u2 = 0; u2 < 2; ++u2) {
-        if (EXACT_V) {
-          dequant_word<T16>(lo2[u2], v_scale, vb0[2 * u2], vb0[2 * u2 + 1]);
-          dequant_word<T16>(hi2[u2], v_scale, vb1[2 * u2], vb1[2 * u2 + 1]);
-        } else {
-          codes_word_to_f16x2(lo2[u2], vb0[2 * u2], vb0[2 * u2 + 1]);
-          codes_word_to_f16x2(hi2[u2], vb1[2 * u2], vb1[2 * u2 + 1]);
-        }
-      }
+      ldsm8_x2_trans(w, row_addr + (((2 * q + (lane >> 4)) ^ (kk & 7)) << 4));
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const uint32_t b0 = vb0[u], b1 = vb1[u];
+        uint32_t b0, b1;
+        const uint32_t codes = PARTIAL ? (w[u] & live) : w[u];
+        if (EXACT_V) dequant_word<T16>(codes, v_scale, b0, b1);
+        else codes_word_to_f16x2(codes, b0, b1);
         Mma16<TP>::run(st.o[4 * q + u], pa[b][0], pa[b][1], pa[b][2], pa[b][3], b0, b1);
       }
     }
@@ -171,7 +233,13 @@ struct KvFp8Traits {
   static constexpr int kWarps = WARPS_;  // consumer warps: two per SM sub-partition; with 256-key
                                          // tiles each owns 32 keys (two independent 16-key blocks)
   static constexpr int kGroups = 1;
-  static constexpr int kMoStride = 128 + 4;  // floats per merge row
+  // Merge rows are unpadded (every byte counts: three 64 KB stages plus these rows just fit
+  // into shared memory); an XOR of the 8-float column group with the row keeps the float2
+  // stores of different rows on different banks.
+  static constexpr int kMoStride = 128;
+  __device__ static __forceinline__ int mo_index(int row, int col) {
+    return row * kMoStride + (col ^ ((row & 7) << 3));
+  }
   static constexpr int kMergeBatch = 8;      // partials merged per L2 round trip
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
@@ -209,10 +277,8 @@ struct KvFp8Traits {
       qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(row1 + d + 2) : 0u;
     }
   }
-  // Accumulator tile nt = 4q + u, thread column c, element e holds d = 32q + 4(2c+e) + u.
-  __device__ static __forceinline__ int out_col(int nt, int c, int e) {
-    return 32 * (nt >> 2) + 4 * (2 * c + e) + (nt & 3);
-  }
+  // d index of accumulator element (n-tile nt, thread column c, element e).
+  __device__ static __forceinline__ int out_col(int nt, int c, int e) { return 8 * nt + 2 * c + e; }
 };
 
 }  // namespace gqa

@@ -96,6 +96,16 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
                : "r"(addr));
 }
 
+// Two 16 x 16 byte matrices, transposed on load (8-bit elements).  Lanes 0-15 give the
+// addresses of the 16 rows (16 bytes each) of matrix 0, lanes 16-31 those of matrix 1.
+// Lane t receives, for matrix m, r[2m] = column t/4 and r[2m+1] = column t/4 + 8, each
+// holding rows 4*(t%4) .. 4*(t%4)+3 in bytes 0..3.
+__device__ __forceinline__ void ldsm8_x2_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
 template <typename T>
 struct Mma16;
 // D(16x8,f32) += A(16x16) * B(16x8); A row-major fragments a0..a3, B col fragments b0,b1.
