@@ -418,9 +418,9 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
 // warpgroup and 224 for the consumers.
 template <class Tr>
 struct BlockShape {
-  static constexpr int kProducerWarps = Tr::kWarps >= 8 ? 4 : 1;
+  static constexpr int kProducerWarps = Tr::kWarps == 8 ? 4 : 1;
   static constexpr int kThreads = (Tr::kWarps + kProducerWarps) * 32;
-  static constexpr bool kRebalanceRegs = Tr::kWarps >= 8;
+  static constexpr bool kRebalanceRegs = Tr::kWarps == 8;
 };
 
 // Stage index and use parity of the next tile (it % nst and (it / nst) & 1 without the
@@ -842,11 +842,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
 
   // -------------------------------------------------------------- consumers
-  if constexpr (BlockShape<Tr>::kRebalanceRegs) {
-    // 8 consumer warps: 12 warps x 168 at launch -> 224; 12 consumer warps: 16 x 128 -> 152
-    if constexpr (Tr::kWarps == 12) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-  }
+  if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
   const bool dynamic = prm.sched.num_splits == 0 && prm.sched.steal;

@@ -145,50 +145,30 @@ __device__ __forceinline__ void consume_block_fp8(uint32_t k_base, uint32_t v_ba
   float s[2 * NB][4];
 #pragma unroll
   for (int t = 0; t < 2 * NB; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
-#ifndef GQA_FP8_KBATCH
-#define GQA_FP8_KBATCH 0
-#endif
-#if GQA_FP8_KBATCH
+  // K: two score tiles (eight words) are dequantised per batch, stage by stage.
+  constexpr int kBatch = 2;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
 #pragma unroll
-    for (int t0 = 0; t0 < 2 * NB; t0 += GQA_FP8_KBATCH) {
-      uint32_t ww[4 * GQA_FP8_KBATCH], bb[8 * GQA_FP8_KBATCH];
+    for (int t0 = 0; t0 < 2 * NB; t0 += kBatch) {
+      uint32_t ww[4 * kBatch], bb[8 * kBatch];
 #pragma unroll
-      for (int t = 0; t < GQA_FP8_KBATCH; ++t) {
+      for (int t = 0; t < kBatch; ++t) {
         const int key = key0 + 8 * (t0 + t) + n;
         const uint4 w = lds128(k_base + key * 128 + (((2 * c + i) ^ (key & 7)) << 4));
         ww[4 * t] = w.x, ww[4 * t + 1] = w.y, ww[4 * t + 2] = w.z, ww[4 * t + 3] = w.w;
       }
-      dequant_words<T16, 4 * GQA_FP8_KBATCH>(ww, k_scale, bb);
+      dequant_words<T16, 4 * kBatch>(ww, k_scale, bb);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int ks = 4 * i + u;
 #pragma unroll
-        for (int t = 0; t < GQA_FP8_KBATCH; ++t)
+        for (int t = 0; t < kBatch; ++t)
           Mma16<T16>::run(s[t0 + t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], bb[8 * t + 2 * u],
                           bb[8 * t + 2 * u + 1]);
       }
     }
   }
-#else
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-#pragma unroll
-    for (int t = 0; t < 2 * NB; ++t) {
-      const int key = key0 + 8 * t + n;
-      const uint4 w = lds128(k_base + key * 128 + (((2 * c + i) ^ (key & 7)) << 4));
-      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int ks = 4 * i + u;
-        uint32_t b0, b1;
-        dequant_word<T16>(ww[u], k_scale, b0, b1);
-        Mma16<T16>::run(s[t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-      }
-    }
-  }
-#endif
   uint32_t pa[NB][4];
   softmax_block<TP, D, UPPER, PARTIAL, NB>(s, st, pa, scale_log2, key0, valid, lane);
   // O += P V.  V fragments come from the byte-transposing ldmatrix: the 16 row addresses of
