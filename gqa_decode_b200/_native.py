@@ -45,6 +45,19 @@ class DecodeArgs(ctypes.Structure):
     ]
 
 
+class AppendArgs(ctypes.Structure):
+    """Mirror of gqa_append_args_t."""
+
+    _fields_ = [
+        ("k_new", c_void_p), ("v_new", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+        ("k_scale", c_void_p), ("v_scale", c_void_p), ("positions", c_void_p),
+        ("block_table", c_void_p), ("saturated", c_void_p),
+        ("batch", c_int32), ("num_kv_heads", c_int32), ("head_dim", c_int32),
+        ("max_seq_len", c_int32), ("src_dtype", c_int32), ("kv_layout", c_int32),
+        ("page_size", c_int32), ("block_table_stride", c_int32), ("stream", c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "gqa_decode_version": (c_char_p, []),
@@ -66,6 +79,7 @@ SIGNATURES = {
          c_void_p]),
     "gqa_quantize_kv_fp8": (
         ctypes.c_int, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "gqa_quantize_append_fp8": (ctypes.c_int, [POINTER(AppendArgs)]),
     "gqa_exchange_buffer_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "gqa_exchange_merge": (
         ctypes.c_int,

@@ -646,6 +646,45 @@ int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64
   return (int)cudaGetLastError();
 }
 
+int gqa_quantize_append_fp8(const gqa_append_args_t* a) {
+  if (!a || !a->k_new || !a->v_new || !a->k_cache || !a->v_cache || !a->k_scale || !a->v_scale ||
+      !a->positions || a->batch <= 0 || a->num_kv_heads <= 0 || a->max_seq_len <= 0)
+    return GQA_ERR_ARG;
+  if (a->head_dim <= 0 || a->head_dim % 4 || a->head_dim > 1024) return GQA_ERR_SHAPE;
+  if (a->src_dtype != GQA_DTYPE_BF16 && a->src_dtype != GQA_DTYPE_FP16) return GQA_ERR_SHAPE;
+  const bool paged = a->kv_layout == GQA_LAYOUT_PAGED_HND || a->kv_layout == GQA_LAYOUT_PAGED_NHD;
+  if (!paged && a->kv_layout != GQA_LAYOUT_PADDED) return GQA_ERR_ARG;
+  if (paged && (!a->block_table || a->page_size <= 0 || a->block_table_stride <= 0 ||
+                (long long)a->block_table_stride * a->page_size < a->max_seq_len))
+    return GQA_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->k_new) & 7) || (reinterpret_cast<uintptr_t>(a->v_new) & 7) ||
+      (reinterpret_cast<uintptr_t>(a->k_cache) & 3) || (reinterpret_cast<uintptr_t>(a->v_cache) & 3))
+    return GQA_ERR_ARG;
+  AppendParams p;
+  p.k_new = a->k_new;
+  p.v_new = a->v_new;
+  p.k_cache = static_cast<uint8_t*>(a->k_cache);
+  p.v_cache = static_cast<uint8_t*>(a->v_cache);
+  p.k_scale = a->k_scale;
+  p.v_scale = a->v_scale;
+  p.positions = a->positions;
+  p.block_table = a->block_table;
+  p.saturated = a->saturated;
+  p.num_kv_heads = a->num_kv_heads;
+  p.head_dim = a->head_dim;
+  p.max_seq = a->max_seq_len;
+  p.layout = a->kv_layout;
+  p.page_size = a->page_size;
+  p.table_stride = a->block_table_stride;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  const unsigned grid = (unsigned)((long long)a->batch * a->num_kv_heads);
+  if (a->src_dtype == GQA_DTYPE_BF16)
+    append_quantize_kernel<__nv_bfloat16><<<grid, a->head_dim / 4, 0, st>>>(p);
+  else
+    append_quantize_kernel<__half><<<grid, a->head_dim / 4, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
 size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim) {
   if (world <= 0 || rows <= 0 || head_dim <= 0) return 0;
   return exchange_buffer_bytes(world, rows, head_dim);

@@ -9,6 +9,7 @@
 #include <cuda_fp8.h>
 
 #include "ptx.cuh"
+#include "schedule.cuh"
 
 namespace gqa {
 
@@ -73,6 +74,65 @@ quantize_kernel(const T16* __restrict__ x, long long elems_per_group, const floa
     }
     q[i] = make_uint2(out[0], out[1]);
   }
+}
+
+// Append one token per sequence to E4M3 caches whose per-(sequence, head) scales are
+// already fixed: code = e4m3(clamp(float(x) / amax * 448, +-448)) with amax = scale * 448,
+// i.e. the arithmetic above with the stored scale (values beyond the head's range saturate
+// and are counted).  One block per (sequence, KV head), four elements per thread.
+struct AppendParams {
+  const void* k_new;       // [batch, Hkv, D] 16-bit
+  const void* v_new;
+  uint8_t* k_cache;        // E4M3 codes, padded or paged layout
+  uint8_t* v_cache;
+  const float* k_scale;    // [batch * Hkv]
+  const float* v_scale;
+  const int* positions;    // [batch] row the token goes to
+  const int* block_table;  // paged layouts
+  int* saturated;          // optional counter of clamped elements
+  int num_kv_heads, head_dim, max_seq, layout, page_size, table_stride;
+};
+
+template <typename T16>
+__global__ void append_quantize_kernel(const AppendParams p) {
+  const int g = blockIdx.x, b = g / p.num_kv_heads, h = g % p.num_kv_heads;
+  const int pos = __ldg(p.positions + b);
+  if (pos < 0 || pos >= p.max_seq) return;  // nothing to write: the caller sized the cache
+  long long row;  // row of D codes inside the cache
+  if (p.layout == kLayoutPadded) {
+    row = (long long)g * p.max_seq + pos;
+  } else {
+    const int page = __ldg(p.block_table + (long long)b * p.table_stride + pos / p.page_size);
+    const int off = pos % p.page_size;
+    row = p.layout == kLayoutPagedHnd
+              ? ((long long)page * p.num_kv_heads + h) * p.page_size + off
+              : ((long long)page * p.page_size + off) * p.num_kv_heads + h;
+  }
+  const int d = 4 * threadIdx.x;
+  int clamped = 0;
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const T16* src = static_cast<const T16*>(which ? p.v_new : p.k_new) + (long long)g * p.head_dim + d;
+    uint8_t* dst = (which ? p.v_cache : p.k_cache) + row * p.head_dim + d;
+    const float a = fmaxf(__fmul_rn(__ldg((which ? p.v_scale : p.k_scale) + g), 448.f), 1e-12f);
+    const uint2 v = *reinterpret_cast<const uint2*>(src);
+    const uint32_t w[2] = {v.x, v.y};
+    uint32_t out = 0u;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const T16 lo = *reinterpret_cast<const T16*>(&w[j]);
+      const T16 hi = *(reinterpret_cast<const T16*>(&w[j]) + 1);
+      float f0 = __fmul_rn(__fdiv_rn(Mma16<T16>::to_float(lo), a), 448.f);
+      float f1 = __fmul_rn(__fdiv_rn(Mma16<T16>::to_float(hi), a), 448.f);
+      clamped += (fabsf(f0) > 448.f) + (fabsf(f1) > 448.f);
+      f0 = fminf(fmaxf(f0, -448.f), 448.f);
+      f1 = fminf(fmaxf(f1, -448.f), 448.f);
+      const unsigned short pr = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
+      out |= (uint32_t)pr << (16 * j);
+    }
+    *reinterpret_cast<uint32_t*>(dst) = out;
+  }
+  if (p.saturated && clamped) atomicAdd(p.saturated, clamped);
 }
 
 }  // namespace gqa

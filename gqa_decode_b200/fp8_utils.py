@@ -61,3 +61,69 @@ def dequantize_kv_fp8(k_fp8, v_fp8, k_scale, v_scale):
     k = (k_fp8.float() * k_scale.view(h, 1, 1)).to(torch.bfloat16)
     v = (v_fp8.float() * v_scale.view(h, 1, 1)).to(torch.bfloat16)
     return k, v
+
+
+def append_kv_fp8(k_new, v_new, k_cache, v_cache, k_scale, v_scale, positions, *,
+                  layout: str = "padded", block_table=None, saturated=None):
+    """Quantise one new token per sequence into E4M3 caches in place (the reference has
+    only the whole-cache :func:`quantize_kv_fp8`; a decode loop needs this between steps).
+
+    k_new/v_new ``[B, Hkv, D]`` bf16/fp16; caches ``float8_e4m3fn`` in the padded layout
+    ``[B, Hkv, Smax, D]`` or paged (``"paged_hnd"`` ``[pages, Hkv, page, D]``, ``"paged_nhd"``
+    ``[pages, page, Hkv, D]`` with ``block_table`` int32 ``[B, max_pages]``); scales fp32
+    ``[B, Hkv]`` as produced when the prompt was quantised; ``positions`` int32 ``[B]`` = the row
+    each token is written to (the sequence length before the append).  Same arithmetic as
+    ``quantize_kv_fp8`` with ``amax = scale * 448``; values outside a head's range saturate
+    (``saturated``, an optional int32 device scalar, counts them).  CUDA only.
+    """
+    import ctypes
+
+    from . import _native
+
+    lib = _native.load()
+    if not (k_new.is_cuda and k_cache.is_cuda):
+        raise ValueError("All tensors must be CUDA tensors")
+    if k_new.dtype not in (torch.bfloat16, torch.float16) or v_new.dtype != k_new.dtype:
+        raise ValueError("Only fp16 and bf16 are supported")
+    if k_cache.dtype != torch.float8_e4m3fn or v_cache.dtype != torch.float8_e4m3fn:
+        raise ValueError("K/V must be float8_e4m3fn")
+    if k_new.dim() != 3 or k_new.shape != v_new.shape or k_cache.shape != v_cache.shape:
+        raise ValueError("Expected k_new/v_new=(batch, num_kv_heads, head_dim) and equal cache shapes")
+    batch, hkv, d = k_new.shape
+    a = _native.AppendArgs()
+    if layout == "padded":
+        if k_cache.dim() != 4 or tuple(k_cache.shape[:2]) != (batch, hkv) or k_cache.shape[3] != d:
+            raise ValueError("padded layout expects caches=(batch, num_kv_heads, max_seq, head_dim)")
+        a.kv_layout, a.max_seq_len = _native.LAYOUT_PADDED, k_cache.shape[2]
+    elif layout in ("paged_hnd", "paged_nhd"):
+        if k_cache.dim() != 4 or block_table is None or block_table.dtype != torch.int32:
+            raise ValueError("paged layouts expect 4-D caches and an int32 block_table")
+        hnd = layout == "paged_hnd"
+        page = k_cache.shape[2] if hnd else k_cache.shape[1]
+        if (k_cache.shape[1] if hnd else k_cache.shape[2]) != hkv or k_cache.shape[3] != d:
+            raise ValueError("cache shape does not match k_new")
+        block_table = block_table.contiguous()
+        a.kv_layout = _native.LAYOUT_PAGED_HND if hnd else _native.LAYOUT_PAGED_NHD
+        a.page_size, a.block_table_stride = page, block_table.shape[1]
+        a.max_seq_len = block_table.shape[1] * page
+        a.block_table = block_table.data_ptr()
+    else:
+        raise ValueError("layout must be 'padded', 'paged_hnd' or 'paged_nhd'")
+    if positions.dtype != torch.int32 or positions.numel() != batch or not positions.is_cuda:
+        raise ValueError("positions must be an int32 CUDA tensor of shape [batch]")
+    if k_scale.numel() != batch * hkv or v_scale.numel() != batch * hkv or k_scale.dtype != torch.float32:
+        raise ValueError("Scales must be float32 [batch, num_kv_heads]")
+    if not (k_new.is_contiguous() and v_new.is_contiguous() and k_cache.is_contiguous()
+            and v_cache.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous")
+    k_scale, v_scale, positions = k_scale.contiguous(), v_scale.contiguous(), positions.contiguous()
+    a.k_new, a.v_new = k_new.data_ptr(), v_new.data_ptr()
+    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    a.k_scale, a.v_scale = k_scale.data_ptr(), v_scale.data_ptr()
+    a.positions = positions.data_ptr()
+    a.saturated = saturated.data_ptr() if saturated is not None else None
+    a.batch, a.num_kv_heads, a.head_dim = batch, hkv, d
+    a.src_dtype = _native.DTYPE_BF16 if k_new.dtype == torch.bfloat16 else _native.DTYPE_FP16
+    a.stream = torch.cuda.current_stream(k_new.device).cuda_stream
+    with torch.cuda.device(k_new.device):
+        _native.check(lib.gqa_quantize_append_fp8(ctypes.byref(a)), "gqa_quantize_append_fp8")

@@ -195,6 +195,36 @@ int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64
                         uint8_t* codes, float* scales, float* amax_scratch, void* stream);
 
 /*
+ * Append one token per sequence to E4M3 caches with fixed per-(sequence, head) scales: the
+ * step a decode loop runs between two gqa_decode_attention_fp8 calls (the reference only
+ * quantises whole caches, gqa_decode/fp8_utils.py:8-43).  Arithmetic of quantize_kv_fp8 with
+ * amax = scale * 448; elements outside the head's range saturate at +-448 and are counted.
+ * The token of sequence b is written to row positions[b] (normally the length before the
+ * append); rows outside [0, max_seq_len) are skipped.
+ */
+typedef struct gqa_append_args {
+  const void* k_new;           /* [batch, num_kv_heads, head_dim], src_dtype (bf16 or fp16) */
+  const void* v_new;
+  void* k_cache;               /* E4M3 codes: GQA_LAYOUT_PADDED or GQA_LAYOUT_PAGED_* */
+  void* v_cache;
+  const float* k_scale;        /* device [batch * num_kv_heads] */
+  const float* v_scale;
+  const int32_t* positions;    /* device [batch] */
+  const int32_t* block_table;  /* paged layouts: device [batch, block_table_stride] */
+  int32_t* saturated;          /* optional device counter, incremented per clamped element */
+  int32_t batch;
+  int32_t num_kv_heads;
+  int32_t head_dim;            /* multiple of 4, at most 1024 */
+  int32_t max_seq_len;         /* rows per head slab (padded), bound on positions */
+  int32_t src_dtype;
+  int32_t kv_layout;
+  int32_t page_size;
+  int32_t block_table_stride;
+  void* stream;
+} gqa_append_args_t;
+int gqa_quantize_append_fp8(const gqa_append_args_t* args);
+
+/*
  * Sequence-shard exchange over NVLink, fused with the merge (no counterpart in the
  * reference, which is single-GPU): every rank calls this once per decode step after its
  * local kernel wrote (local_o [rows, head_dim] fp32, local_lse [rows]).  peer_bufs is a

@@ -113,6 +113,15 @@ def dequantize_kv_e4m3(k8, v8, k_scale, v_scale):
     return kd, vd
 
 
+def append_codes_e4m3(x_new: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """E4M3 codes of new rows under an existing per-head scale: the arithmetic of
+    gqa_decode/fp8_utils.py:32-41 with amax = scale * 448 (fp32).  The reference has no
+    append step; this restates what a cache that keeps its prompt-time scales must do.
+    x_new [..., D] with one scale per leading index (scale.shape == x_new.shape[:-1])."""
+    amax = (scale.float() * 448.0).clamp(min=1e-12).unsqueeze(-1)
+    return (x_new.float() / amax * 448.0).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+
+
 def attend_one_sequence_e4m3(q, k8, v8, k_scale, v_scale):
     """The FP8 oracle the reference's tests use (tests/test_fp8.py:37-41):
     dequantise to bf16, then run the exact attention."""

@@ -216,3 +216,87 @@ def test_paged_argument_errors(G):
     with pytest.raises(ValueError):
         G.gqa_decode_attention_batched(qd, kpd, vpd, sl, layout="paged_hnd", block_table=td,
                                        max_seq_len=10 ** 6)
+
+
+@pytest.mark.parametrize("layout", ["padded", "paged_hnd", "paged_nhd"])
+def test_append_token_fp8(G, layout):
+    """Decode loop on an E4M3 cache: quantise the prompt, then append tokens one step at a time
+    with the prompt's scales.  Codes must equal the CPU restatement bit for bit, the rest of
+    the cache must stay untouched, and decoding over the grown cache must stay inside the
+    tolerance of dequantise -> oracle."""
+    from gqa_decode_b200 import fp8_utils
+
+    hq, hkv, d, page, smax = 32, 8, 128, 16, 512
+    lens = [100, 255, 31, 1]
+    steps = 3
+    g = torch.Generator().manual_seed(3)
+    q = O.randn_bf16((len(lens), hq, d), g)
+    full_k = [O.randn_bf16((hkv, l + steps, d), g) for l in lens]
+    full_v = [O.randn_bf16((hkv, l + steps, d), g) for l in lens]
+    # one appended value far outside the prompt's range: must saturate and be counted
+    full_k[0][2, lens[0] + 1, 5] = 1000.0
+    quant = [fp8_utils.quantize_kv_fp8(k[:, :l].contiguous(), v[:, :l].contiguous())
+             for k, v, l in zip(full_k, full_v, lens)]
+    ksc = torch.stack([x[2] for x in quant])
+    vsc = torch.stack([x[3] for x in quant])
+    # reference codes of every row under the prompt scales (rows < len are the prompt itself)
+    want_k = [torch.cat([quant[b][0], O.append_codes_e4m3(
+        full_k[b][:, lens[b]:], ksc[b][:, None].expand(-1, steps))], 1) for b in range(len(lens))]
+    want_v = [torch.cat([quant[b][1], O.append_codes_e4m3(
+        full_v[b][:, lens[b]:], vsc[b][:, None].expand(-1, steps))], 1) for b in range(len(lens))]
+    u8 = lambda t: t.view(torch.uint8)
+    if layout == "padded":
+        K = torch.full((len(lens), hkv, smax, d), 0x55, dtype=torch.uint8)
+        V = K.clone()
+        for b, l in enumerate(lens):
+            K[b, :, :l], V[b, :, :l] = u8(quant[b][0]), u8(quant[b][1])
+        table = None
+    else:
+        # pages for the final lengths; rows past the prompt hold a marker byte
+        grown_k = [torch.cat([u8(quant[b][0]), torch.full((hkv, steps, d), 0x55, dtype=torch.uint8)], 1)
+                   for b in range(len(lens))]
+        grown_v = [torch.cat([u8(quant[b][1]), torch.full((hkv, steps, d), 0x55, dtype=torch.uint8)], 1)
+                   for b in range(len(lens))]
+        K, V, table = _pages(grown_k, grown_v, page, layout, seed=6, poison=float(0x55), smax=smax)
+    Kd, Vd = K.to(DEV).view(torch.float8_e4m3fn), V.to(DEV).view(torch.float8_e4m3fn)
+    td = table.to(DEV) if table is not None else None
+    sat = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    kw = dict(layout=layout, block_table=td) if td is not None else {}
+    dkw = dict(kw, max_seq_len=smax) if td is not None else {}
+    for step in range(steps):
+        kn = torch.stack([full_k[b][:, lens[b] + step] for b in range(len(lens))]).to(DEV)
+        vn = torch.stack([full_v[b][:, lens[b] + step] for b in range(len(lens))]).to(DEV)
+        fp8_utils.append_kv_fp8(kn, vn, Kd, Vd, ksc.to(DEV), vsc.to(DEV), sl, saturated=sat, **kw)
+        sl += 1
+        out = G.gqa_decode_attention_batched(q.to(DEV), Kd, Vd, sl, k_scale=ksc.to(DEV),
+                                             v_scale=vsc.to(DEV), **dkw)
+        assert G.read_status() == 0
+        n = [l + step + 1 for l in lens]
+        ref = torch.stack([O.attend_one_sequence_e4m3(
+            q[b], want_k[b][:, :n[b]], want_v[b][:, :n[b]], ksc[b], vsc[b]) for b in range(len(lens))])
+        ok, ratio, mx = within_tolerance(out.cpu(), ref)
+        assert ok, f"step {step}: worst |d|/tol = {ratio:.3f}, max abs {mx:.3e}"
+    # clamped elements: the planted outlier plus whatever exceeds a short prompt's range
+    expect = 0
+    for b, l in enumerate(lens):
+        for x, sc in ((full_k[b], ksc[b]), (full_v[b], vsc[b])):
+            f = x[:, l:].float() / (sc * 448.0).clamp(min=1e-12)[:, None, None] * 448.0
+            expect += int((f.abs() > 448.0).sum())
+    assert expect >= 1 and int(sat.item()) == expect
+    # every written row equals the CPU restatement; everything else still holds the marker / prompt
+    Kc, Vc = Kd.view(torch.uint8).cpu(), Vd.view(torch.uint8).cpu()
+    for b, l in enumerate(lens):
+        for r in range(l + steps + 1):
+            if layout == "padded":
+                gk, gv = Kc[b, :, r], Vc[b, :, r]
+            else:
+                pg, off = int(table[b, r // page]), r % page
+                if r >= l + steps and (r // page) >= (l + steps + page - 1) // page:
+                    break  # past the last allocated page
+                gk = Kc[pg, :, off] if layout == "paged_hnd" else Kc[pg, off]
+                gv = Vc[pg, :, off] if layout == "paged_hnd" else Vc[pg, off]
+            if r < l + steps:
+                assert torch.equal(gk, u8(want_k[b])[:, r]) and torch.equal(gv, u8(want_v[b])[:, r]), (b, r)
+            else:
+                assert (gk == 0x55).all() and (gv == 0x55).all(), (b, r)
