@@ -57,7 +57,7 @@ class Workload:
     """Device-resident inputs of one rank plus the callable that runs one step."""
 
     def __init__(self, name: str, rank: int, world: int, dev: torch.device, batch: int = 16,
-                 exchange: str = "nvlink"):
+                 exchange: str = "nvlink", gather: str = "none"):
         import gqa_decode_b200 as G
 
         self.G, self.name, self.rank, self.world, self.dev = G, name, rank, world, dev
@@ -159,6 +159,23 @@ class Workload:
         esz = 1 if self.fp8 else 2
         self.bytes_per_step = 2 * hkv_local * sum(self.lens) * d * esz  # this rank, K + V only
         self.step_index = 0
+        self.gather = gather if name in ("headshard", "headshard_fp8") and world > 1 else "none"
+        self.head_gather = None
+        if self.gather == "fused":
+            from gqa_decode_b200.distributed import HeadGather
+
+            self.head_gather = HeadGather(self.q.shape[0], self.q.shape[1], d, torch.bfloat16, dev)
+            self.collective = "outputs gathered on every rank inside the decode kernel (peer stores + flags)"
+            self.desc["parallelism"] = f"tp{world} (KV heads, fused output gather)"
+        elif self.gather == "nccl":
+            import torch.distributed as dist
+
+            self.dist = dist
+            self.collective = "NCCL all-gather of the bf16 outputs after the decode kernel"
+            self.launches_per_step = 2
+            self.gathered = torch.empty(world * self.q.shape[0], self.q.shape[1], d,
+                                        dtype=torch.bfloat16, device=dev)
+            self.desc["parallelism"] = f"tp{world} (KV heads, NCCL output all-gather)"
         self.exchange = None
         if name == "seqshard" and world > 1 and exchange == "nvlink":
             from gqa_decode_b200.distributed import NvlinkExchange
@@ -190,6 +207,8 @@ class Workload:
             self.desc["launch"] = "one CUDA graph per K/V buffer set, replayed"
         elif self.name == "seqshard" and self.world > 1:
             self.plan = G.plan_decode(self.q, self.k, self.v, None, return_f32=True, return_lse=True)
+        elif self.head_gather is not None:
+            self.gather_step = self.head_gather.plan(self.q, self.k, self.v, self.seq_lens, **self.kw)
         else:
             self.plan = G.plan_decode(self.q, self.k, self.v, self.seq_lens, **self.kw)
 
@@ -209,7 +228,13 @@ class Workload:
             w = self.world
             return G.merge_partials(self.gather_o.view(w, -1, 128), self.gather_l.view(w, -1),
                                     out_dtype=torch.bfloat16)
-        return self.plan.run()
+        if self.head_gather is not None:
+            return self.gather_step()
+        out = self.plan.run()
+        if self.gather == "nccl":
+            self.dist.all_gather_into_tensor(self.gathered, out)
+            return self.gathered
+        return out
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -353,6 +378,9 @@ def main():
                          "state (0 for profiler runs).  Kept short: after about 0.3 s of continuous "
                          "streaming the B200s of this pool settle about 8 %% below their burst "
                          "bandwidth, and the roofline peak in MEASURED_PEAKS.json is a burst figure")
+    ap.add_argument("--gather", default="none", choices=["none", "fused", "nccl"],
+                    help="headshard at N>1: leave outputs sharded, gather them inside the decode kernel, "
+                         "or all-gather them with NCCL afterwards")
     ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
                     help="seqshard at N>1: fused peer-store exchange+merge kernel, or NCCL all-gather + merge")
     ap.add_argument("--no-e2e", action="store_true")
@@ -406,7 +434,7 @@ def main():
     _native.load()
     import gqa_decode_b200 as G
 
-    wl = Workload(args.workload, rank, world, dev, args.batch, args.exchange)
+    wl = Workload(args.workload, rank, world, dev, args.batch, args.exchange, args.gather)
     wl.prepare()
     sampler = ClockSampler(local_rank)
 

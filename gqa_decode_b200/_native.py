@@ -45,6 +45,15 @@ class DecodeArgs(ctypes.Structure):
     ]
 
 
+class GatherArgs(ctypes.Structure):
+    """Mirror of gqa_gather_args_t."""
+
+    _fields_ = [
+        ("peer_out", POINTER(c_void_p)), ("peer_flags", POINTER(c_void_p)),
+        ("world", c_int32), ("rank", c_int32), ("epoch", ctypes.c_uint32),
+    ]
+
+
 class AppendArgs(ctypes.Structure):
     """Mirror of gqa_append_args_t."""
 
@@ -79,6 +88,7 @@ SIGNATURES = {
          c_void_p]),
     "gqa_quantize_kv_fp8": (
         ctypes.c_int, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "gqa_decode_attention_gather": (ctypes.c_int, [POINTER(DecodeArgs), POINTER(GatherArgs)]),
     "gqa_quantize_append_fp8": (ctypes.c_int, [POINTER(AppendArgs)]),
     "gqa_exchange_buffer_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "gqa_exchange_merge": (

@@ -200,8 +200,23 @@ static std::atomic<unsigned long long*> g_timestamp_buffer{nullptr};
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced) {
-  if (!a || !a->q || !a->k || !a->v || (!a->out && !a->out_f32) || !a->workspace) return GQA_ERR_ARG;
+static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced,
+                      const gqa_gather_args_t* gather = nullptr) {
+  if (!a || !a->q || !a->k || !a->v || !a->workspace) return GQA_ERR_ARG;
+  if (!gather && !a->out && !a->out_f32) return GQA_ERR_ARG;
+  if (gather) {
+    if (gather->world < 1 || gather->world > kMaxPeers || gather->rank < 0 ||
+        gather->rank >= gather->world || gather->epoch == 0 || !gather->peer_out ||
+        !gather->peer_flags)
+      return GQA_ERR_ARG;
+    for (int p = 0; p < gather->world; ++p)
+      if (!gather->peer_out[p] || !gather->peer_flags[p] || !aligned16(gather->peer_out[p]))
+        return GQA_ERR_ARG;
+    // the hand-off is part of the decode kernel's tail: it needs the in-kernel merge, and the
+    // finished-CTA counter it uses is the work-stealing clean-up's
+    if (a->flags & (GQA_FLAG_SEPARATE_MERGE | GQA_FLAG_NO_MERGE | GQA_FLAG_WORK_STEALING))
+      return GQA_ERR_ARG;
+  }
   if (a->batch <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->max_seq_len <= 0 ||
       a->total_rows <= 0 || a->num_splits < 0 || a->num_ctas < 0)
     return GQA_ERR_ARG;
@@ -319,6 +334,15 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   if (paged && (a->page_size & (a->page_size - 1)) == 0)
     for (prm.page_shift = 0; (1 << prm.page_shift) < a->page_size;) ++prm.page_shift;
 
+  if (gather) {
+    for (int p = 0; p < gather->world; ++p) {
+      prm.gather_out[p] = gather->peer_out[p];
+      prm.gather_flags[p] = gather->peer_flags[p];
+    }
+    prm.gather_world = gather->world;
+    prm.gather_rank = gather->rank;
+    prm.gather_epoch = gather->epoch;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   if (workspace_needs_clear(a->workspace, w.lse_off)) {
     cudaError_t e = cudaMemsetAsync(a->workspace, 0, w.lse_off, st);
@@ -548,6 +572,11 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args) {
 }
 
 int gqa_decode_attention_fp8(const gqa_decode_args_t* args) { return run_decode(args, true, false); }
+
+int gqa_decode_attention_gather(const gqa_decode_args_t* args, const gqa_gather_args_t* gather) {
+  if (!args || !gather) return GQA_ERR_ARG;
+  return run_decode(args, args->kv_dtype == GQA_DTYPE_E4M3, false, gather);
+}
 
 // ---- entry for callers that cannot allocate: scratch inside the library image ----------
 // The array's name is only a host-side handle in host code; kernels must be given the

@@ -27,6 +27,7 @@ namespace gqa {
 constexpr int kMaxConsumerWarps = 8;
 constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kernel
 constexpr int kMaxStages = 8;
+constexpr int kMaxPeers = 8;  // GPUs of one NVLink domain that can gather head-sharded outputs
 constexpr int kDescRing = 32;  // tile descriptors kept in shared memory (>= 4 * kMaxStages)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -37,6 +38,7 @@ enum StatusBits : int {
   kStatusWaitEmpty = 2,   // the producer gave up waiting for a free stage
   kStatusSmemAlign = 4,   // shared memory base not 1024-byte aligned
   kStatusSlotRange = 8,   // a partial slot index fell outside the workspace (write skipped)
+  kStatusWaitExchange = 16,  // a peer GPU's flag never arrived (sequence exchange, head gather)
 };
 
 struct DecodeParams {
@@ -74,6 +76,13 @@ struct DecodeParams {
   int box_rows;             // rows per TMA box: min(tile, page_size), a power of two
   int box_shift;            // log2(box_rows)
   int page_shift;           // log2(page_size), or -1 when page_size is not a power of two
+  // head-sharded launches that gather their outputs on every rank (gather_world > 0): final
+  // rows go to every rank's [batch, gather_world * Hq, D] buffer by peer stores, at this rank's
+  // head offset; the last CTA then raises this rank's flag on every peer and waits for theirs
+  void* gather_out[kMaxPeers];
+  unsigned* gather_flags[kMaxPeers];  // every rank's [2 parities][world] flag words
+  int gather_world, gather_rank;
+  unsigned gather_epoch;
 };
 
 // What the producer tells the consumers about the tile in a pipeline stage.
@@ -295,7 +304,17 @@ struct Kv16Traits {
 template <typename Q, int D>
 __device__ __forceinline__ void store_final(const DecodeParams& prm, long long out_row, int d4,
                                             float4 v) {
-  if (prm.out) {
+  if (prm.gather_world > 0) {
+    // row (b, head) of this rank is row (b, rank * Hq + head) of the gathered tensor
+    const long long b = out_row / prm.num_q_heads, hd = out_row % prm.num_q_heads;
+    const long long grow =
+        (b * prm.gather_world + prm.gather_rank) * (long long)prm.num_q_heads + hd;
+    uint2 pk;
+    pk.x = Mma16<Q>::pack(v.x, v.y);
+    pk.y = Mma16<Q>::pack(v.z, v.w);
+    for (int p = 0; p < prm.gather_world; ++p)
+      *reinterpret_cast<uint2*>(reinterpret_cast<Q*>(prm.gather_out[p]) + grow * D + 4 * d4) = pk;
+  } else if (prm.out) {
     Q* o = reinterpret_cast<Q*>(prm.out) + out_row * D + 4 * d4;
     uint2 pk;
     pk.x = Mma16<Q>::pack(v.x, v.y);
@@ -1069,6 +1088,37 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     ts[4] = (unsigned long long)(clock64() - cc0);
   }
 #endif
+  if (prm.gather_world > 0) {
+    // Hand-off of the gathered outputs: every thread's peer stores are fenced at system scope,
+    // the last CTA to get here raises this rank's flag on every peer (release) and waits,
+    // bounded, until every peer's flag for this epoch has arrived: when the kernel ends, the
+    // whole [batch, world * Hq, D] tensor is complete in this rank's buffer.
+    __threadfence_system();
+    bar_sync(1, kConsumerThreads);
+    if (tid == 0) {
+      const int before = atom_add_acq_rel(prm.done_ctas, 1);
+      if (before == (int)gridDim.x - 1) {
+        *prm.done_ctas = 0;
+        __threadfence_system();
+        const unsigned par = prm.gather_epoch & 1u;
+        const int w = prm.gather_world;
+        for (int p = 0; p < w; ++p)
+          st_release_sys(prm.gather_flags[p] + par * w + prm.gather_rank, prm.gather_epoch);
+        const unsigned* mine = prm.gather_flags[prm.gather_rank] + par * w;
+        const unsigned long long t0 = global_timer_ns();
+        for (int p = 0; p < w; ++p) {
+          while (ld_acquire_sys(mine + p) != prm.gather_epoch) {
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+              atomicOr(prm.status, kStatusWaitExchange);
+              p = w;
+              break;
+            }
+            __nanosleep(100);
+          }
+        }
+      }
+    }
+  }
   if (tid == 0) {
     if (prm.timestamps) prm.timestamps[3 * blockIdx.x + 2] = global_timer_ns();
     // work stealing only: the last CTA to finish leaves the chunk deques clean for the

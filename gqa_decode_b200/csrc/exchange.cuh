@@ -36,7 +36,6 @@ struct ExchangeParams {
   float* out_lse;          // optional
   int* status;             // optional device word: |= kStatusWaitExchange on expiry
 };
-constexpr int kStatusWaitExchange = 16;
 constexpr int kExchangeThreads = 256;
 
 __host__ __device__ inline size_t exchange_header_bytes(int world) {
@@ -47,15 +46,6 @@ __host__ __device__ inline size_t exchange_slot_floats(long long rows, int D) {
 }
 __host__ __device__ inline size_t exchange_buffer_bytes(int world, long long rows, int D) {
   return exchange_header_bytes(world) + 2 * (size_t)world * exchange_slot_floats(rows, D) * sizeof(float);
-}
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
 }
 
 template <typename Q>

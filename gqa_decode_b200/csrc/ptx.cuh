@@ -168,6 +168,16 @@ __device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
   return old;
 }
 
+// System-scope release / acquire on flags that peers (other GPUs over NVLink) write or read.
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float ld_cg_f32(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ float4 ld_cg_f32x4(const float4* p) { return __ldcg(p); }
 

@@ -109,6 +109,99 @@ class NvlinkExchange:
         return int(self.status.item())
 
 
+class HeadGather:
+    """Head-sharded decode whose outputs land, inside the decode kernel itself, in every
+    rank's ``[B, world * Hq_local, D]`` buffer (``gqa_decode_attention_gather``): the
+    all-gather a tensor-parallel layer would run after attention disappears.  Final rows are
+    written with plain peer stores; the kernel's last CTA raises this rank's flag on every
+    peer and waits (bounded) for theirs, so ``decode()`` returns a tensor that is complete
+    once the stream reaches that point.  Two output buffers alternate by step parity, so a
+    rank may start step e+1 while a slower peer still reads step e.
+
+    Collective constructor: every rank of ``group`` creates it with the same ``batch``,
+    ``local_q_heads`` (query heads per rank), ``head_dim`` and ``dtype``.  One process per GPU,
+    one NVLink domain, at most 8 ranks.  No multicast, no NVLS."""
+
+    def __init__(self, batch: int, local_q_heads: int, head_dim: int, dtype: torch.dtype, device,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _native
+
+        _native.load()
+        self._native, self._ctypes = _native, ctypes
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks can gather head-sharded outputs")
+        self.device = torch.device(device)
+        self.shape = (int(batch), self.world * int(local_q_heads), int(head_dim))
+        elems = self.shape[0] * self.shape[1] * self.shape[2]
+        self.out = symm_mem.empty(2 * elems, dtype=dtype, device=self.device)
+        self.flags = symm_mem.empty(2 * self.world, dtype=torch.int32, device=self.device)
+        self.flags.zero_()  # epochs start at 1
+        self._out_handle = symm_mem.rendezvous(self.out, self.group)
+        self._flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        esz = self.out.element_size()
+        ptr_array = ctypes.c_void_p * self.world
+        # [parity] -> host array of every rank's output buffer for that parity
+        self._peer_out = [
+            ptr_array(*[int(self._out_handle.buffer_ptrs[r]) + par * elems * esz
+                        for r in range(self.world)]) for par in (0, 1)]
+        self._peer_flags = ptr_array(*[int(self._flag_handle.buffer_ptrs[r]) for r in range(self.world)])
+        self.epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every flag array is zeroed before anybody raises a flag in it
+
+    def _next(self, g):
+        """Advance to the next step: bump the epoch and point `g` at that parity's buffers."""
+        ctypes = self._ctypes
+        self.epoch += 1
+        par = self.epoch & 1
+        g.peer_out = ctypes.cast(self._peer_out[par], ctypes.POINTER(ctypes.c_void_p))
+        g.peer_flags = ctypes.cast(self._peer_flags, ctypes.POINTER(ctypes.c_void_p))
+        g.world, g.rank, g.epoch = self.world, self.rank, self.epoch
+        elems = self.shape[0] * self.shape[1] * self.shape[2]
+        return self.out[par * elems:(par + 1) * elems].view(self.shape)
+
+    def plan(self, q_local, k_local, v_local, seq_lens=None, **kw):
+        """Validate once; the returned callable runs one step (one C call) and returns the
+        gathered ``[B, world * Hq_local, D]`` tensor of that step."""
+        from .gqa_decode import plan_decode
+
+        g = self._native.GatherArgs()
+        self._next(g)
+        self.epoch -= 1  # nothing ran yet
+        inner = plan_decode(q_local, k_local, v_local, seq_lens, _gather=g, **kw)
+
+        def run():
+            view = self._next(g)
+            inner.run()
+            return view
+
+        return run
+
+    def decode(self, q_local, k_local, v_local, seq_lens=None, **kw) -> torch.Tensor:
+        """q_local ``[B, Hq_local, D]``, k/v the local KV heads (any layout that
+        :func:`gqa_decode_attention_batched` accepts).  Returns ``[B, world * Hq_local, D]``:
+        rank r's heads at ``[:, r * Hq_local:(r + 1) * Hq_local]`` (valid until the step after
+        next overwrites the buffer)."""
+        from .gqa_decode import gqa_decode_attention_batched
+
+        n = self._native
+        if tuple(q_local.shape) != (self.shape[0], self.shape[1] // self.world, self.shape[2]):
+            raise ValueError("q_local does not match the gather's batch / heads / head_dim")
+        if q_local.dtype != self.out.dtype:
+            raise ValueError("q dtype does not match the gather's dtype")
+        g = n.GatherArgs()
+        view = self._next(g)
+        gqa_decode_attention_batched(q_local, k_local, v_local, seq_lens, _gather=g, **kw)
+        return view
+
+
 def sequence_sharded_decode(
     q: torch.Tensor,
     k_shard: torch.Tensor,

@@ -176,6 +176,7 @@ def gqa_decode_attention_batched(
     _entry: str = "auto",
     _no_merge: bool = False,
     _plan_only: bool = False,
+    _gather=None,
 ):
     """One decode step for a batch of sequences with individual KV lengths.
 
@@ -295,13 +296,16 @@ def gqa_decode_attention_batched(
     ws = workspace if workspace is not None else _workspace(dev, need)
     if ws.numel() * ws.element_size() < need:
         raise ValueError(f"workspace too small: need {need} bytes")
-    if out is None:
+    if _gather is not None:
+        out = None  # final rows go to the gathered buffers of every rank (distributed.HeadGather)
+    elif out is None:
         out = torch.empty_like(q)
     out_f32 = torch.empty(q.shape, dtype=torch.float32, device=dev) if return_f32 else None
     out_lse = torch.empty(q.shape[:2], dtype=torch.float32, device=dev) if return_lse else None
 
     a = _native.DecodeArgs()
-    a.q, a.k, a.v, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+    a.q, a.k, a.v = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    a.out = out.data_ptr() if out is not None else None
     a.out_f32 = out_f32.data_ptr() if out_f32 is not None else None
     a.out_lse = out_lse.data_ptr() if out_lse is not None else None
     a.seq_lens = seq_lens.data_ptr() if seq_lens is not None else None
@@ -323,7 +327,11 @@ def gqa_decode_attention_batched(
     if code_layout >= _native.LAYOUT_PAGED_HND:
         a.block_table = block_table.data_ptr()
         a.page_size, a.block_table_stride = page_size, block_table.shape[1]
-    if fp8:
+    if _gather is not None:
+        gather_ref = ctypes.byref(_gather)
+        entry = lib.gqa_decode_attention_gather
+        fn = lambda ref: entry(ref, gather_ref)  # noqa: E731
+    elif fp8:
         fn = lib.gqa_decode_attention_fp8
     elif _entry == "persistent":
         fn = lib.gqa_decode_attention_persistent
@@ -332,7 +340,8 @@ def gqa_decode_attention_batched(
     extras = tuple(t for t in (out_f32, out_lse) if t is not None)
     result = (out, *extras) if extras else out
     if _plan_only:
-        keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse, block_table)
+        keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse, block_table,
+                _gather)
         return DecodePlan(fn, a, dev, result, keep)
     with torch.cuda.device(dev):
         _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")

@@ -195,6 +195,32 @@ int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64
                         uint8_t* codes, float* scales, float* amax_scratch, void* stream);
 
 /*
+ * Head-sharded decode whose outputs are gathered on every rank inside the same kernel (no
+ * counterpart in the reference, which is single-GPU; this is the hand-off a tensor-parallel
+ * layer otherwise does with an all-gather after attention).  Rank r of `world` runs its KV
+ * heads exactly as gqa_decode_attention[_fp8] would (args->num_q_heads / num_kv_heads are the
+ * LOCAL head counts, args->out is ignored) and writes every final row with plain peer stores
+ * into every rank's [batch, world * num_q_heads, head_dim] buffer at head offset
+ * r * num_q_heads.  The last CTA then raises flag[epoch parity][r] = epoch on every peer
+ * (release, system scope) and waits - bounded, status bit 16 on expiry - for every peer's
+ * flag, so that when the kernel ends the gathered tensor in this rank's buffer is complete.
+ * peer_out / peer_flags are HOST arrays of `world` device pointers as mapped in this process
+ * (symmetric memory); flags are 2 * world uint32 per rank, zero before the first call;
+ * epoch starts at 1 and grows by one per call, the same on all ranks.  Callers alternate
+ * between two output buffers by epoch parity when consecutive steps may overlap across
+ * ranks.  Needs the in-kernel merge and the static schedule (no GQA_FLAG_SEPARATE_MERGE,
+ * _NO_MERGE, _WORK_STEALING); world <= 8.  No multicast, no NVLS: plain loads and stores.
+ */
+typedef struct gqa_gather_args {
+  void* const* peer_out;
+  uint32_t* const* peer_flags;
+  int32_t world;
+  int32_t rank;
+  uint32_t epoch;
+} gqa_gather_args_t;
+int gqa_decode_attention_gather(const gqa_decode_args_t* args, const gqa_gather_args_t* gather);
+
+/*
  * Append one token per sequence to E4M3 caches with fixed per-(sequence, head) scales: the
  * step a decode loop runs between two gqa_decode_attention_fp8 calls (the reference only
  * quantises whole caches, gqa_decode/fp8_utils.py:8-43).  Arithmetic of quantize_kv_fp8 with

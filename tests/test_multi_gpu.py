@@ -51,6 +51,27 @@ def _worker(rank, world, port, result_dir):
     outh = D.head_sharded_decode(q[:, qs].contiguous().to(dev), k[:, hs].contiguous().to(dev),
                                  v[:, hs].contiguous().to(dev), sl, gather_output=True)
     errs["heads"] = float((outh.float() - whole.float()).abs().max())
+    # the same hand-off fused into the decode kernel (peer stores + flags), bf16 and FP8,
+    # several steps in a row (epochs, alternating output buffers)
+    hg = D.HeadGather(b, hq // world, d, torch.bfloat16, dev)
+    ql, kl, vl = q[:, qs].contiguous().to(dev), k[:, hs].contiguous().to(dev), v[:, hs].contiguous().to(dev)
+    worst, same = 0.0, True
+    for it in range(4):
+        got = hg.decode(ql, kl, vl, sl)
+        worst = max(worst, float((got.float() - whole.float()).abs().max()))
+        same = same and torch.equal(got, outh)  # same local launches as the NCCL-gathered result
+    errs["gather"], errs["gather_same"] = worst, same
+    from gqa_decode_b200 import fp8_utils
+    quant = [fp8_utils.quantize_kv_fp8(k[i].to(dev), v[i].to(dev)) for i in range(b)]
+    k8 = torch.stack([x[0] for x in quant]); v8 = torch.stack([x[1] for x in quant])
+    ksc = torch.stack([x[2] for x in quant]); vsc = torch.stack([x[3] for x in quant])
+    whole8 = G.gqa_decode_attention_batched(q.to(dev), k8, v8, sl, k_scale=ksc, v_scale=vsc)
+    got8 = hg.decode(ql, k8[:, hs].contiguous(), v8[:, hs].contiguous(), sl,
+                     k_scale=ksc[:, hs].contiguous(), v_scale=vsc[:, hs].contiguous())
+    errs["gather_fp8"] = float((got8.float() - whole8.float()).abs().max())
+    local8 = G.gqa_decode_attention_batched(ql, k8[:, hs].contiguous(), v8[:, hs].contiguous(), sl,
+                                            k_scale=ksc[:, hs].contiguous(), v_scale=vsc[:, hs].contiguous())
+    errs["gather_fp8_same"] = torch.equal(got8[:, qs], local8)
     errs["status"] = G.read_status()
     torch.save(errs, os.path.join(result_dir, f"errs_{rank}.pt"))
     dist.barrier()
@@ -70,3 +91,42 @@ def test_two_gpu_sharded_decode(tmp_path):
         # same partials, same merge arithmetic: shard results differ from the whole only by
         # float32 rounding, far below one bf16 ulp of the O(0.1) outputs
         assert e["nvlink"] < 2e-3 and e["nccl"] < 2e-3 and e["heads"] < 2e-3, e
+        # the fused hand-off moves the bits of the local launches (a different split schedule
+        # than the whole-batch launch, hence the last-ulp difference to `whole`)
+        assert e["gather_same"] and e["gather_fp8_same"], e
+        assert e["gather"] < 2e-3 and e["gather_fp8"] < 2e-3, e
+
+
+def _single_rank_gather(rank, port, result_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    import gqa_decode_b200 as G
+    from gqa_decode_b200 import distributed as D
+
+    g = torch.Generator().manual_seed(11)
+    b, hq, hkv, d, s = 3, 32, 8, 128, 4096
+    mk = lambda *sh: torch.randn(*sh, generator=g).to(torch.bfloat16)
+    q, k, v = mk(b, hq, d).to(dev), mk(b, hkv, s, d).to(dev), mk(b, hkv, s, d).to(dev)
+    sl = torch.tensor([s, 0, 777], dtype=torch.int32, device=dev)
+    want = G.gqa_decode_attention_batched(q, k, v, sl)
+    hg = D.HeadGather(b, hq, d, torch.bfloat16, dev)
+    same = all(torch.equal(hg.decode(q, k, v, sl), want) for _ in range(3))
+    torch.save({"same": same, "status": G.read_status()}, os.path.join(result_dir, "single.pt"))
+    dist.destroy_process_group()
+
+
+def test_head_gather_single_rank(tmp_path):
+    """World of one: the gather path (peer stores into the own buffer, flag raise and wait in
+    the kernel's tail) must reproduce the plain launch bit for bit."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_single_rank_gather, args=(_free_port(), str(tmp_path)), nprocs=1, join=True)
+    r = torch.load(os.path.join(tmp_path, "single.pt"))
+    assert r["same"] and r["status"] == 0, r
