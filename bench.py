@@ -12,6 +12,7 @@ Workloads (synthetic, seeded; shapes of the five benchmark configurations):
                  (default; every rank runs its own batch: weak scaling, no collective)
   single         B=1  Hq=32 Hkv=8 D=128 bf16 S=16384
   fp8            B=8  Hq=32 Hkv=8 D=128 E4M3 S=32768, 0.1 % outliers x20
+  paged          config 2 with K/V in shuffled 64-row pages + block table
   seqshard       B=1  Hq=64 Hkv=8 D=128 bf16 S=131072 split into N contiguous sequence shards,
                  (O, LSE) all-gathered with NCCL and merged on device (strong scaling)
   headshard      B=64 Hq=64 Hkv=8 D=128 bf16 S=8192, KV heads split over N ranks (strong)
@@ -57,7 +58,7 @@ class Workload:
     """Device-resident inputs of one rank plus the callable that runs one step."""
 
     def __init__(self, name: str, rank: int, world: int, dev: torch.device, batch: int = 16,
-                 exchange: str = "nvlink", gather: str = "none"):
+                 exchange: str = "nvlink", gather: str = "none", page_size: int = 64):
         import gqa_decode_b200 as G
 
         self.G, self.name, self.rank, self.world, self.dev = G, name, rank, world, dev
@@ -80,6 +81,28 @@ class Workload:
             self.desc = {"workload": "ragged_batch_decode(config 2)", "batch": batch, "num_q_heads": hq,
                          "num_kv_heads": hkv, "head_dim": d, "kv_dtype": "bf16",
                          "seq_lens": self.lens, "kv_layout": "packed", "parallelism": f"replica x{world}"}
+        elif name == "paged":
+            # config 2's ragged batch held the way serving engines hold it: a pool of
+            # 64-row pages [pages, Hkv, 64, D] handed out in shuffled order, plus a block table
+            self.lens = make_lengths(1234 + rank, batch)
+            hq, hkv, page = 32, 8, page_size
+            need = [(l + page - 1) // page for l in self.lens]
+            pages = sum(need)
+            self.q = rn(batch, hq, d).to(torch.bfloat16)
+            self.k = rn(pages, hkv, page, d).to(torch.bfloat16)
+            self.v = rn(pages, hkv, page, d).to(torch.bfloat16)
+            order = torch.randperm(pages, generator=gen, device=dev).to(torch.int32)
+            table = torch.zeros(batch, max(need), dtype=torch.int32, device=dev)
+            at = 0
+            for i, n in enumerate(need):
+                table[i, :n] = order[at:at + n]
+                at += n
+            self.seq_lens = torch.tensor(self.lens, dtype=torch.int32, device=dev)
+            self.kw = dict(layout="paged_hnd", block_table=table, max_seq_len=max(need) * page)
+            self.desc = {"workload": "ragged_batch_decode(config 2), paged KV", "batch": batch,
+                         "num_q_heads": hq, "num_kv_heads": hkv, "head_dim": d, "kv_dtype": "bf16",
+                         "seq_lens": self.lens, "kv_layout": f"paged_hnd, {page} rows per page, shuffled",
+                         "parallelism": f"replica x{world}"}
         elif name == "single":
             hq, hkv, s = 32, 8, 16384
             self.lens = [s]
@@ -313,7 +336,7 @@ def make_cpu_sample(name: str, budget_keys: int):
     from oracle import gqa_oracle as O
 
     g = torch.Generator().manual_seed(1234)
-    if name in ("ragged",):
+    if name in ("ragged", "paged"):
         lens, hq, hkv = make_lengths(1234), 32, 8
     elif name == "single":
         lens, hq, hkv = [16384], 32, 8
@@ -371,7 +394,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="ragged",
-                    choices=["ragged", "single", "fp8", "seqshard", "headshard", "headshard_fp8"])
+                    choices=["ragged", "paged", "single", "fp8", "seqshard", "headshard", "headshard_fp8"])
+    ap.add_argument("--page-size", type=int, default=64, help="paged workload: rows per page")
     ap.add_argument("--batch", type=int, default=16, help="ragged workload only: sequences per rank")
     ap.add_argument("--preheat-s", type=float, default=0.05,
                     help="seconds of untimed steps after the warm-up so the SM clock leaves its idle "
@@ -434,7 +458,7 @@ def main():
     _native.load()
     import gqa_decode_b200 as G
 
-    wl = Workload(args.workload, rank, world, dev, args.batch, args.exchange, args.gather)
+    wl = Workload(args.workload, rank, world, dev, args.batch, args.exchange, args.gather, args.page_size)
     wl.prepare()
     sampler = ClockSampler(local_rank)
 
@@ -443,16 +467,27 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up: W steps plus a short run so the SM clock is at its loaded level
+    # warm-up: W steps plus a short run so the SM clock is at its loaded level.  The number of
+    # extra steps is agreed between the ranks (steps with an exchange are collective: every
+    # rank must run the same count), from the slowest rank's estimate of a step.
     for _ in range(max(3, args.warmup)):
         wl.step()
     torch.cuda.synchronize()
     sampler.start()
-    t0 = time.perf_counter()
-    while time.perf_counter() - t0 < args.preheat_s:
-        for _ in range(20):
-            wl.step()
-        torch.cuda.synchronize()
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record()
+    for _ in range(5):
+        wl.step()
+    w1.record()
+    torch.cuda.synchronize()
+    est_ms = max(w0.elapsed_time(w1) / 5, 1e-3)
+    extra = torch.tensor([min(int(args.preheat_s * 1e3 / est_ms) + 1, 100000) if args.preheat_s > 0 else 0],
+                         device=dev, dtype=torch.int64)
+    if world > 1:
+        dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+    for _ in range(int(extra.item())):
+        wl.step()
+    torch.cuda.synchronize()
 
     # ---- device-resident timing
     barrier()
