@@ -58,7 +58,7 @@ class Workload:
     """Device-resident inputs of one rank plus the callable that runs one step."""
 
     def __init__(self, name: str, rank: int, world: int, dev: torch.device, batch: int = 16,
-                 exchange: str = "nvlink", gather: str = "none", page_size: int = 64):
+                 exchange: str = "fused", gather: str = "none", page_size: int = 64):
         import gqa_decode_b200 as G
 
         self.G, self.name, self.rank, self.world, self.dev = G, name, rank, world, dev
@@ -205,6 +205,13 @@ class Workload:
 
             self.exchange = NvlinkExchange(hq, d, dev)
             self.collective = "fused NVLink push + flag + merge kernel (peer stores, symmetric memory)"
+        self.fused_exchange = None
+        if name == "seqshard" and world > 1 and exchange == "fused":
+            from gqa_decode_b200.distributed import FusedSequenceExchange
+
+            self.fused_exchange = FusedSequenceExchange(1, hq, d, dev)
+            self.collective = "exchange and merge inside the decode kernel (peer stores + flags, symmetric memory)"
+            self.launches_per_step = 1
         if name == "seqshard" and world > 1:
             import torch.distributed as dist
 
@@ -228,6 +235,8 @@ class Workload:
                     p.run()
                 self.graphs.append(g)
             self.desc["launch"] = "one CUDA graph per K/V buffer set, replayed"
+        elif self.fused_exchange is not None:
+            self.fused_step = self.fused_exchange.plan(self.q, self.k, self.v, None)
         elif self.name == "seqshard" and self.world > 1:
             self.plan = G.plan_decode(self.q, self.k, self.v, None, return_f32=True, return_lse=True)
         elif self.head_gather is not None:
@@ -242,6 +251,8 @@ class Workload:
             self.step_index += 1
             self.graphs[i].replay()
             return self.plans[i].result
+        if self.fused_exchange is not None:
+            return self.fused_step()
         if self.name == "seqshard" and self.world > 1:
             _, o32, lse = self.plan.run()
             if self.exchange is not None:
@@ -405,8 +416,9 @@ def main():
     ap.add_argument("--gather", default="none", choices=["none", "fused", "nccl"],
                     help="headshard at N>1: leave outputs sharded, gather them inside the decode kernel, "
                          "or all-gather them with NCCL afterwards")
-    ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
-                    help="seqshard at N>1: fused peer-store exchange+merge kernel, or NCCL all-gather + merge")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nvlink", "nccl"],
+                    help="seqshard at N>1: exchange+merge inside the decode kernel, a separate peer-store "
+                         "exchange+merge kernel, or NCCL all-gather + merge")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -13,6 +13,7 @@ from . import build as _build
 
 DTYPE_BF16, DTYPE_FP16, DTYPE_E4M3 = 0, 1, 2
 LAYOUT_PADDED, LAYOUT_PACKED, LAYOUT_PAGED_HND, LAYOUT_PAGED_NHD = 0, 1, 2, 3
+GATHER_HEADS, GATHER_SEQUENCE = 0, 1
 FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
 FLAG_FP8_EXACT_V = 4
@@ -50,7 +51,7 @@ class GatherArgs(ctypes.Structure):
 
     _fields_ = [
         ("peer_out", POINTER(c_void_p)), ("peer_flags", POINTER(c_void_p)),
-        ("world", c_int32), ("rank", c_int32), ("epoch", ctypes.c_uint32),
+        ("world", c_int32), ("rank", c_int32), ("epoch", ctypes.c_uint32), ("mode", c_int32),
     ]
 
 

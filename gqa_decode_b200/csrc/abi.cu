@@ -203,8 +203,9 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced,
                       const gqa_gather_args_t* gather = nullptr) {
   if (!a || !a->q || !a->k || !a->v || !a->workspace) return GQA_ERR_ARG;
-  if (!gather && !a->out && !a->out_f32) return GQA_ERR_ARG;
+  if ((!gather || gather->mode == GQA_GATHER_SEQUENCE) && !a->out && !a->out_f32) return GQA_ERR_ARG;
   if (gather) {
+    if (gather->mode != GQA_GATHER_HEADS && gather->mode != GQA_GATHER_SEQUENCE) return GQA_ERR_ARG;
     if (gather->world < 1 || gather->world > kMaxPeers || gather->rank < 0 ||
         gather->rank >= gather->world || gather->epoch == 0 || !gather->peer_out ||
         !gather->peer_flags)
@@ -342,6 +343,8 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     prm.gather_world = gather->world;
     prm.gather_rank = gather->rank;
     prm.gather_epoch = gather->epoch;
+    prm.gather_mode = gather->mode;
+    prm.gather_rows = (long long)a->batch * a->num_q_heads;
   }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   if (workspace_needs_clear(a->workspace, w.lse_off)) {

@@ -83,6 +83,12 @@ struct DecodeParams {
   unsigned* gather_flags[kMaxPeers];  // every rank's [2 parities][world] flag words
   int gather_world, gather_rank;
   unsigned gather_epoch;
+  // gather_mode 1 (sequence sharding): gather_out[p] is rank p's receive area of floats,
+  // [2 parities][source rank][rows * D outputs, rows log-sum-exps]; every rank's normalised
+  // fp32 rows and LSEs are pushed there, and after the flags every CTA merges its share of
+  // the rows from the `world` partials now in local memory into out / out_f32 / out_lse
+  int gather_mode;
+  long long gather_rows;    // batch * Hq
 };
 
 // What the producer tells the consumers about the tile in a pipeline stage.
@@ -304,6 +310,15 @@ struct Kv16Traits {
 template <typename Q, int D>
 __device__ __forceinline__ void store_final(const DecodeParams& prm, long long out_row, int d4,
                                             float4 v) {
+  if (prm.gather_world > 0 && prm.gather_mode == 1) {
+    // sequence shard: this rank's normalised fp32 row goes to every rank's receive area
+    const size_t slot = (size_t)prm.gather_rows * (D + 1);
+    const size_t off = ((size_t)(prm.gather_epoch & 1u) * prm.gather_world + prm.gather_rank) * slot +
+                       (size_t)out_row * D + 4 * d4;
+    for (int p = 0; p < prm.gather_world; ++p)
+      *reinterpret_cast<float4*>(static_cast<float*>(prm.gather_out[p]) + off) = v;
+    return;
+  }
   if (prm.gather_world > 0) {
     // row (b, head) of this rank is row (b, rank * Hq + head) of the gathered tensor
     const long long b = out_row / prm.num_q_heads, hd = out_row % prm.num_q_heads;
@@ -322,6 +337,20 @@ __device__ __forceinline__ void store_final(const DecodeParams& prm, long long o
     *reinterpret_cast<uint2*>(o) = pk;
   }
   if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + out_row * D + 4 * d4) = v;
+}
+
+// Natural-log sum-exp of a final row: to the caller's buffer, or (sequence shards) to every
+// rank's receive area next to the row's output.
+template <int D>
+__device__ __forceinline__ void store_final_lse(const DecodeParams& prm, long long out_row, float lse) {
+  if (prm.gather_world > 0 && prm.gather_mode == 1) {
+    const size_t slot = (size_t)prm.gather_rows * (D + 1);
+    const size_t off = ((size_t)(prm.gather_epoch & 1u) * prm.gather_world + prm.gather_rank) * slot +
+                       (size_t)prm.gather_rows * D + out_row;
+    for (int p = 0; p < prm.gather_world; ++p) static_cast<float*>(prm.gather_out[p])[off] = lse;
+    return;
+  }
+  if (prm.out_lse) prm.out_lse[out_row] = lse;
 }
 
 // `lse_smem` (capacity `lse_cap` floats) stages the group's n*G log-sum-exps so that the
@@ -380,8 +409,8 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
       acc.z *= inv;
       acc.w *= inv;
       store_final<Q, D>(prm, out_row0 + row, d4, acc);
-      if (d4 == 0 && prm.out_lse)
-        prm.out_lse[out_row0 + row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
+      if (d4 == 0)
+        store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
       continue;
     }
     float mx = -INFINITY;
@@ -423,8 +452,8 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
     acc.z *= inv;
     acc.w *= inv;
     store_final<Q, D>(prm, out_row0 + row, d4, acc);
-    if (d4 == 0 && prm.out_lse)
-      prm.out_lse[out_row0 + row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
+    if (d4 == 0)
+      store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
   }
 }
 
@@ -873,7 +902,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       for (int idx = tid; idx < Hq * (D / 4); idx += kConsumerThreads) {
         const int row = idx / (D / 4), d4 = idx % (D / 4);
         store_final<Q, D>(prm, (long long)b * Hq + row, d4, make_float4(0.f, 0.f, 0.f, 0.f));
-        if (d4 == 0 && prm.out_lse) prm.out_lse[(long long)b * Hq + row] = -INFINITY;
+        if (d4 == 0) store_final_lse<D>(prm, (long long)b * Hq + row, -INFINITY);
       }
       if (!prm.fused_merge)
         for (int h = tid; h < Hkv; h += kConsumerThreads)
@@ -1040,7 +1069,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         L += sm_ml[(w * grows + tid) * 2 + 1] * fast_exp2(sm_ml[(w * grows + tid) * 2] - Ms);
       const float lse = L > 0.f ? (Ms + fast_log2(L)) * kLn2 : -INFINITY;
       if (direct) {
-        if (prm.out_lse) prm.out_lse[out_row0 + tid] = lse;
+        store_final_lse<D>(prm, out_row0 + tid, lse);
       } else if (slot >= 0) {
         prm.part_lse[(size_t)slot * G + tid] = lse;
       }
@@ -1089,32 +1118,87 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
 #endif
   if (prm.gather_world > 0) {
-    // Hand-off of the gathered outputs: every thread's peer stores are fenced at system scope,
-    // the last CTA to get here raises this rank's flag on every peer (release) and waits,
-    // bounded, until every peer's flag for this epoch has arrived: when the kernel ends, the
-    // whole [batch, world * Hq, D] tensor is complete in this rank's buffer.
+    // Hand-off of the gathered outputs: every thread's peer stores are fenced at system scope;
+    // in the last CTA to get here, thread p raises this rank's flag on peer p (one fence, then
+    // a plain system-scope store: eight release stores in a row would pay eight fences) and
+    // waits, bounded, for peer p's flag of this epoch.  When the kernel ends, the whole
+    // [batch, world * Hq, D] tensor is complete in this rank's buffer.
     __threadfence_system();
     bar_sync(1, kConsumerThreads);
     if (tid == 0) {
       const int before = atom_add_acq_rel(prm.done_ctas, 1);
-      if (before == (int)gridDim.x - 1) {
-        *prm.done_ctas = 0;
-        __threadfence_system();
-        const unsigned par = prm.gather_epoch & 1u;
-        const int w = prm.gather_world;
-        for (int p = 0; p < w; ++p)
-          st_release_sys(prm.gather_flags[p] + par * w + prm.gather_rank, prm.gather_epoch);
-        const unsigned* mine = prm.gather_flags[prm.gather_rank] + par * w;
-        const unsigned long long t0 = global_timer_ns();
-        for (int p = 0; p < w; ++p) {
-          while (ld_acquire_sys(mine + p) != prm.gather_epoch) {
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-              atomicOr(prm.status, kStatusWaitExchange);
-              p = w;
-              break;
-            }
-            __nanosleep(100);
+      const int last = before == (int)gridDim.x - 1;
+      if (last) *prm.done_ctas = 0;
+      *sm_flag = last;
+      sm_flag[2] = 1;
+    }
+    bar_sync(1, kConsumerThreads);
+    const int w = prm.gather_world;
+    const unsigned par = prm.gather_epoch & 1u;
+    if (*sm_flag && tid < w) {
+      __threadfence_system();
+      st_relaxed_sys(prm.gather_flags[tid] + par * w + prm.gather_rank, prm.gather_epoch);
+    }
+    // head gather: only the last CTA has to see the peers' flags before the kernel may end;
+    // sequence shards: every CTA needs all partials before it merges its rows
+    int arrived = 1;
+    if ((*sm_flag || prm.gather_mode == 1) && tid < w) {
+      const unsigned* mine = prm.gather_flags[prm.gather_rank] + par * w + tid;
+      const unsigned long long t0 = global_timer_ns();
+      while (ld_acquire_sys(mine) != prm.gather_epoch) {
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+          atomicOr(prm.status, kStatusWaitExchange);
+          arrived = 0;
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    if (prm.gather_mode == 1) {
+      // LSE-weighted merge of the `world` partials of this CTA's share of the rows (the
+      // algebra of merge_rows_kernel, i.e. of gqa_decode/gqa_decode.py:661-669 one level up)
+      // all partials have landed only if no waiting thread gave up (sm_flag[2]: third word of
+      // the flag area, set to 1 above)
+      if (!arrived) sm_flag[2] = 0;
+      bar_sync(1, kConsumerThreads);
+      if (sm_flag[2]) {
+        constexpr int D4 = D / 4;
+        const long long rows = prm.gather_rows;
+        const size_t slot = (size_t)rows * (D + 1);
+        const float* part = static_cast<const float*>(prm.gather_out[prm.gather_rank]) + (size_t)par * w * slot;
+        const long long r0m = rows * blockIdx.x / gridDim.x, r1m = rows * (blockIdx.x + 1) / gridDim.x;
+        for (long long idx = r0m * D4 + tid; idx < r1m * D4; idx += kConsumerThreads) {
+          const long long row = idx / D4;
+          const int d4 = (int)(idx % D4);
+          float mx = -INFINITY;
+          for (int sidx = 0; sidx < w; ++sidx) mx = fmaxf(mx, __ldcg(part + sidx * slot + (size_t)rows * D + row));
+          const float ms = (mx == -INFINITY) ? 0.f : mx;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          float wsum = 0.f;
+          for (int sidx = 0; sidx < w; ++sidx) {
+            const float l = __ldcg(part + sidx * slot + (size_t)rows * D + row);
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(part + sidx * slot + row * D) + d4);
+            const float wt = fast_exp2((l - ms) * kLog2e);
+            acc.x += wt * o.x;
+            acc.y += wt * o.y;
+            acc.z += wt * o.z;
+            acc.w += wt * o.w;
+            wsum += wt;
           }
+          const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+          acc.x *= inv;
+          acc.y *= inv;
+          acc.z *= inv;
+          acc.w *= inv;
+          if (prm.out) {
+            uint2 pk;
+            pk.x = Mma16<Q>::pack(acc.x, acc.y);
+            pk.y = Mma16<Q>::pack(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<Q*>(prm.out) + row * D + 4 * d4) = pk;
+          }
+          if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + row * D + 4 * d4) = acc;
+          if (prm.out_lse && d4 == 0)
+            prm.out_lse[row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
         }
       }
     }

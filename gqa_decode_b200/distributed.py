@@ -164,6 +164,7 @@ class HeadGather:
         g.peer_out = ctypes.cast(self._peer_out[par], ctypes.POINTER(ctypes.c_void_p))
         g.peer_flags = ctypes.cast(self._peer_flags, ctypes.POINTER(ctypes.c_void_p))
         g.world, g.rank, g.epoch = self.world, self.rank, self.epoch
+        g.mode = self._native.GATHER_HEADS
         elems = self.shape[0] * self.shape[1] * self.shape[2]
         return self.out[par * elems:(par + 1) * elems].view(self.shape)
 
@@ -200,6 +201,85 @@ class HeadGather:
         view = self._next(g)
         gqa_decode_attention_batched(q_local, k_local, v_local, seq_lens, _gather=g, **kw)
         return view
+
+
+class FusedSequenceExchange:
+    """Sequence-sharded decode in ONE kernel per rank and step
+    (``gqa_decode_attention_gather`` with ``GQA_GATHER_SEQUENCE``): while a rank streams its
+    slice of the keys, every finished row (normalised fp32 output + log-sum-exp) is pushed into
+    all ranks' receive areas with plain peer stores; the kernel's tail raises the flags, waits
+    (bounded) for the peers' and merges the ``world`` partials into the final output.  Replaces
+    decode kernel + :class:`NvlinkExchange` kernel (or two NCCL all-gathers + merge).
+
+    Collective constructor (same ``batch``, ``num_q_heads``, ``head_dim`` on every rank); one
+    process per GPU of one NVLink domain, at most 8 ranks.  No multicast, no NVLS."""
+
+    def __init__(self, batch: int, num_q_heads: int, head_dim: int, device,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _native
+
+        _native.load()
+        self._native, self._ctypes = _native, ctypes
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.device = torch.device(device)
+        self.shape = (int(batch), int(num_q_heads), int(head_dim))
+        rows = self.shape[0] * self.shape[1]
+        self.recv = symm_mem.empty(2 * self.world * rows * (self.shape[2] + 1), dtype=torch.float32,
+                                   device=self.device)
+        self.flags = symm_mem.empty(2 * self.world, dtype=torch.int32, device=self.device)
+        self.flags.zero_()
+        self._recv_handle = symm_mem.rendezvous(self.recv, self.group)
+        self._flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        ptr_array = ctypes.c_void_p * self.world
+        self._peer_recv = ptr_array(*[int(self._recv_handle.buffer_ptrs[r]) for r in range(self.world)])
+        self._peer_flags = ptr_array(*[int(self._flag_handle.buffer_ptrs[r]) for r in range(self.world)])
+        self.epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def _next(self, g):
+        ctypes = self._ctypes
+        self.epoch += 1
+        g.peer_out = ctypes.cast(self._peer_recv, ctypes.POINTER(ctypes.c_void_p))
+        g.peer_flags = ctypes.cast(self._peer_flags, ctypes.POINTER(ctypes.c_void_p))
+        g.world, g.rank, g.epoch = self.world, self.rank, self.epoch
+        g.mode = self._native.GATHER_SEQUENCE
+
+    def decode(self, q, k_shard, v_shard, seq_lens_shard=None, **kw) -> torch.Tensor:
+        """q ``[B, Hq, D]`` (identical on all ranks), k/v this rank's keys of every head,
+        ``seq_lens_shard`` how many of them are valid (0 allowed).  Returns the full output
+        ``[B, Hq, D]`` on every rank."""
+        from .gqa_decode import gqa_decode_attention_batched
+
+        if tuple(q.shape) != self.shape:
+            raise ValueError("q does not match the exchange's batch / heads / head_dim")
+        g = self._native.GatherArgs()
+        self._next(g)
+        return gqa_decode_attention_batched(q, k_shard, v_shard, seq_lens_shard, _gather=g, **kw)
+
+    def plan(self, q, k_shard, v_shard, seq_lens_shard=None, **kw):
+        """Validate once; the returned callable runs one step (one C call) and returns the
+        output tensor (the same storage every step)."""
+        from .gqa_decode import plan_decode
+
+        g = self._native.GatherArgs()
+        self._next(g)
+        self.epoch -= 1  # nothing ran yet
+        inner = plan_decode(q, k_shard, v_shard, seq_lens_shard, _gather=g, **kw)
+
+        def run():
+            self._next(g)
+            return inner.run()
+
+        return run
 
 
 def sequence_sharded_decode(

@@ -296,7 +296,7 @@ def gqa_decode_attention_batched(
     ws = workspace if workspace is not None else _workspace(dev, need)
     if ws.numel() * ws.element_size() < need:
         raise ValueError(f"workspace too small: need {need} bytes")
-    if _gather is not None:
+    if _gather is not None and _gather.mode == _native.GATHER_HEADS:
         out = None  # final rows go to the gathered buffers of every rank (distributed.HeadGather)
     elif out is None:
         out = torch.empty_like(q)

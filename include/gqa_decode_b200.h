@@ -211,12 +211,23 @@ int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64
  * ranks.  Needs the in-kernel merge and the static schedule (no GQA_FLAG_SEPARATE_MERGE,
  * _NO_MERGE, _WORK_STEALING); world <= 8.  No multicast, no NVLS: plain loads and stores.
  */
+#define GQA_GATHER_HEADS 0    /* ranks own KV heads; outputs are gathered (described above) */
+#define GQA_GATHER_SEQUENCE 1 /* ranks own contiguous key ranges of every head: rank r's
+                                 normalised fp32 rows and log-sum-exps are pushed into every
+                                 rank's receive area peer_out[p] (floats, [2 parities][world]
+                                 [batch * num_q_heads * (head_dim + 1)]: outputs, then LSEs) as
+                                 they are produced; after the flags every CTA merges its share of
+                                 the rows (LSE-weighted, the reference's reduce_partials algebra,
+                                 gqa_decode/gqa_decode.py:661-669, across ranks) into args->out /
+                                 out_f32 / out_lse of this rank: one kernel per rank and step,
+                                 the exchange overlaps the streaming */
 typedef struct gqa_gather_args {
   void* const* peer_out;
   uint32_t* const* peer_flags;
   int32_t world;
   int32_t rank;
   uint32_t epoch;
+  int32_t mode;               /* GQA_GATHER_* */
 } gqa_gather_args_t;
 int gqa_decode_attention_gather(const gqa_decode_args_t* args, const gqa_gather_args_t* gather);
 

@@ -72,6 +72,12 @@ def _worker(rank, world, port, result_dir):
     local8 = G.gqa_decode_attention_batched(ql, k8[:, hs].contiguous(), v8[:, hs].contiguous(), sl,
                                             k_scale=ksc[:, hs].contiguous(), v_scale=vsc[:, hs].contiguous())
     errs["gather_fp8_same"] = torch.equal(got8[:, qs], local8)
+    # sequence shards again, exchange and merge fused into the decode kernel itself
+    fx = D.FusedSequenceExchange(b, hq, d, dev)
+    for it in range(4):
+        outf = fx.decode(q.to(dev), ks, vs, local_lens)
+    errs["fused_seq"] = float((outf.float() - whole.float()).abs().max())
+    errs["fused_seq_vs_kernel_pair"] = float((outf.float() - out.float()).abs().max())
     errs["status"] = G.read_status()
     torch.save(errs, os.path.join(result_dir, f"errs_{rank}.pt"))
     dist.barrier()
@@ -95,6 +101,7 @@ def test_two_gpu_sharded_decode(tmp_path):
         # than the whole-batch launch, hence the last-ulp difference to `whole`)
         assert e["gather_same"] and e["gather_fp8_same"], e
         assert e["gather"] < 2e-3 and e["gather_fp8"] < 2e-3, e
+        assert e["fused_seq"] < 2e-3 and e["fused_seq_vs_kernel_pair"] < 2e-3, e
 
 
 def _single_rank_gather(rank, port, result_dir):
@@ -116,7 +123,13 @@ def _single_rank_gather(rank, port, result_dir):
     want = G.gqa_decode_attention_batched(q, k, v, sl)
     hg = D.HeadGather(b, hq, d, torch.bfloat16, dev)
     same = all(torch.equal(hg.decode(q, k, v, sl), want) for _ in range(3))
-    torch.save({"same": same, "status": G.read_status()}, os.path.join(result_dir, "single.pt"))
+    # a world of one through the sequence-exchange mode: push to the own receive area, flags,
+    # merge of a single partial (weight exactly 1) - again the plain launch's bits
+    fx = D.FusedSequenceExchange(b, hq, d, dev)
+    same_seq = all(torch.equal(fx.decode(q, k, v, sl), want) for _ in range(3))
+    run = fx.plan(q, k, v, sl)
+    same_seq = same_seq and all(torch.equal(run(), want) for _ in range(2))
+    torch.save({"same": same and same_seq, "status": G.read_status()}, os.path.join(result_dir, "single.pt"))
     dist.destroy_process_group()
 
 
