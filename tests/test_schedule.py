@@ -105,3 +105,17 @@ def test_schedule_random(native_lib):
         layout = int(rng.integers(0, 2))
         rec, _ = dump(native_lib, lens, hkv, max_seq, tile, ctas, splits, layout)
         check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout)
+
+
+@pytest.mark.parametrize("splits", [0, 3])
+def test_paged_layouts_share_the_padded_schedule(native_lib, splits):
+    """Where rows live does not enter the schedule: paged layouts (2, 3) replay to exactly the
+    padded layout's segments and slots (lengths clamped to max_seq alike); only the row base is
+    left to the block table (reported as 0)."""
+    lens = [1, 7, 5000, 0, 2500, 64, 65, 9000]
+    padded, _ = dump(native_lib, lens, 8, 5120, 64, 148, splits, 0)
+    for layout in (2, 3):
+        paged, _ = dump(native_lib, lens, 8, 5120, 64, 148, splits, layout)
+        assert paged.shape == padded.shape
+        assert np.array_equal(paged[:, :8], padded[:, :8])
+        assert (paged[:, 8] == 0).all()
