@@ -18,6 +18,9 @@ FLAG_SEPARATE_MERGE = 1
 FLAG_NO_MERGE = 2
 FLAG_FP8_EXACT_V = 4
 FLAG_WORK_STEALING = 8
+FLAG_CLEAR_WORKSPACE = 16
+FLAG_DEPENDENT_LAUNCH = 32
+TIMESTAMP_WORDS = 6  # uint64 words per CTA in DecodeArgs.debug_timestamps
 STATIC_SCRATCH_BYTES = 16 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {
@@ -43,6 +46,7 @@ class DecodeArgs(ctypes.Structure):
         ("softmax_scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("stream", c_void_p),
         ("block_table", c_void_p), ("page_size", c_int32), ("block_table_stride", c_int32),
+        ("wait_limit_ns", ctypes.c_uint64), ("debug_timestamps", c_void_p),
     ]
 
 
@@ -71,9 +75,10 @@ class AppendArgs(ctypes.Structure):
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "gqa_decode_version": (c_char_p, []),
-    "gqa_debug_set_timestamp_buffer": (ctypes.c_int, [c_void_p]),
     "gqa_decode_tile_rows": (ctypes.c_int, [c_int32, c_int32]),
     "gqa_decode_workspace_bytes": (
+        ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
+    "gqa_decode_workspace_control_bytes": (
         ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
     "gqa_decode_workspace_layout": (
         ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
@@ -95,7 +100,7 @@ SIGNATURES = {
     "gqa_exchange_merge": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_void_p, c_int32, c_int32, ctypes.c_uint32, c_int64, c_int32,
-         c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+         c_void_p, c_int32, c_void_p, c_void_p, c_void_p, ctypes.c_uint64, c_void_p]),
     "gqa_select_num_splits": (ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "gqa_schedule_dump": (
         c_int64,
@@ -111,7 +116,9 @@ _lib = None
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """Path of the shared library: the in-tree build, or the file named by the environment
+    variable GQA_DECODE_B200_LIB (a differently configured build of the same sources)."""
+    return os.environ.get("GQA_DECODE_B200_LIB") or _build.LIB_PATH
 
 
 def load() -> ctypes.CDLL:

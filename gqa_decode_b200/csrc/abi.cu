@@ -4,7 +4,6 @@
 
 #include <atomic>
 #include <cmath>
-#include <mutex>
 #include <cstdio>
 #include <cstring>
 
@@ -152,9 +151,24 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
     if (e != cudaSuccess) return (int)e;
     configured.fetch_or(bit, std::memory_order_release);
   }
-  decode_kernel<Tr><<<num_ctas, BlockShape<Tr>::kThreads, smem, stream>>>(tk, tv, prm);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)num_ctas);
+  cfg.blockDim = dim3((unsigned)BlockShape<Tr>::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (prm.pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  e = cudaLaunchKernelEx(&cfg, decode_kernel<Tr>, tk, tv, prm);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return (int)e;
+  }
   if (separate_merge) {
     merge_groups_kernel<typename Tr::Q, Tr::D>
         <<<(unsigned)groups, kMergeThreads, 0, stream>>>(prm);
@@ -164,44 +178,12 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
   return 0;
 }
 
-// The control words at the front of a workspace (deques, tickets, counters) must be zero
-// when a launch starts.  Kernels leave them zero, but their extent depends on the batch
-// geometry, and a launch with a different geometry may find old partial data where its
-// control words live.  The library therefore remembers, per workspace pointer, the extent
-// it last left clean and clears the control region again whenever it changes (or the
-// pointer is new).
-struct WorkspaceNote {
-  const void* ptr;
-  size_t ctrl_bytes;
-};
-static std::mutex g_ws_mutex;
-static WorkspaceNote g_ws_notes[64];
-static unsigned g_ws_next = 0;
-
-static bool workspace_needs_clear(const void* ptr, size_t ctrl_bytes) {
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
-  for (auto& n : g_ws_notes)
-    if (n.ptr == ptr) {
-      if (n.ctrl_bytes == ctrl_bytes) return false;
-      n.ctrl_bytes = ctrl_bytes;
-      return true;
-    }
-  g_ws_notes[g_ws_next++ % 64] = WorkspaceNote{ptr, ctrl_bytes};
-  return true;
-}
-static void workspace_forget(const void* ptr) {
-  std::lock_guard<std::mutex> lock(g_ws_mutex);
-  for (auto& n : g_ws_notes)
-    if (n.ptr == ptr) n = WorkspaceNote{nullptr, 0};
-}
-
-// Diagnostics: when set, every decode launch records per-CTA timestamps there.
-static std::atomic<unsigned long long*> g_timestamp_buffer{nullptr};
-
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// `clear_control`: zero the workspace's control words on the stream once every check has
+// passed (GQA_FLAG_CLEAR_WORKSPACE asks for the same).
 static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced,
-                      const gqa_gather_args_t* gather = nullptr) {
+                      const gqa_gather_args_t* gather = nullptr, bool clear_control = false) {
   if (!a || !a->q || !a->k || !a->v || !a->workspace) return GQA_ERR_ARG;
   if ((!gather || gather->mode == GQA_GATHER_SEQUENCE) && !a->out && !a->out_f32) return GQA_ERR_ARG;
   if (gather) {
@@ -324,7 +306,9 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   prm.fused_merge = fused ? 1 : 0;
   prm.no_merge = no_merge ? 1 : 0;
   prm.num_slots = (int)w.slots;
-  prm.timestamps = g_timestamp_buffer.load(std::memory_order_relaxed);
+  prm.timestamps = reinterpret_cast<unsigned long long*>(a->debug_timestamps);
+  prm.wait_limit_ns = a->wait_limit_ns ? a->wait_limit_ns : kDefaultWaitLimitNs;
+  prm.pdl = (a->flags & GQA_FLAG_DEPENDENT_LAUNCH) ? 1 : 0;
   prm.block_table = paged ? a->block_table : nullptr;
   prm.page_size = paged ? a->page_size : 0;
   prm.table_stride = paged ? a->block_table_stride : 0;
@@ -347,7 +331,7 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     prm.gather_rows = (long long)a->batch * a->num_q_heads;
   }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
-  if (workspace_needs_clear(a->workspace, w.lse_off)) {
+  if (clear_control || (a->flags & GQA_FLAG_CLEAR_WORKSPACE)) {
     cudaError_t e = cudaMemsetAsync(a->workspace, 0, w.lse_off, st);
     if (e != cudaSuccess) return (int)e;
   }
@@ -499,12 +483,6 @@ using namespace gqa;
 
 extern "C" {
 
-int gqa_debug_set_timestamp_buffer(uint64_t* device_buffer) {
-  g_timestamp_buffer.store(reinterpret_cast<unsigned long long*>(device_buffer),
-                           std::memory_order_relaxed);
-  return 0;
-}
-
 const char* gqa_decode_version(void) { return "gqa_decode_b200 0.1 (sm_100a)"; }
 
 int gqa_decode_tile_rows(int32_t head_dim, int32_t kv_dtype) {
@@ -526,6 +504,19 @@ int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_k
   long long slots = default_balanced_slots(groups, ctas);
   if (groups * num_splits > slots) slots = groups * num_splits;
   *bytes = layout_workspace(groups, ctas, slots, num_q_heads / num_kv_heads, head_dim).total + 512;
+  return 0;
+}
+
+int gqa_decode_workspace_control_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                       int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                                       size_t* bytes) {
+  if (!bytes || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
+      num_splits < 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
+    return GQA_ERR_ARG;
+  const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(1024);
+  // the control words end where the partial log-sum-exps begin, whatever the slot count
+  *bytes = layout_workspace((long long)batch * num_kv_heads, ctas, 0, num_q_heads / num_kv_heads,
+                            head_dim).lse_off;
   return 0;
 }
 
@@ -551,11 +542,8 @@ int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_
 
 int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace || workspace_bytes < 512) return GQA_ERR_ARG;
-  // status word + counters sit at the front; partial slots need no initialisation.
-  // The counter region is bounded by the first 256-byte boundary after them, but its
-  // size depends on the batch, so clear everything up to the partials conservatively:
-  // tickets are only ever non-zero inside a launch, so clearing more is harmless.
-  workspace_forget(workspace);
+  // Only the control words need to be zero, but how far they reach depends on the geometry
+  // of the next launch, which is not known here: clear everything.
   cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream));
   return (int)e;
 }
@@ -616,13 +604,13 @@ int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args) {
   const WorkspaceLayout w = layout_workspace(groups, ctas, need_slots, G, args->head_dim);
   if (w.total + 512 > (size_t)GQA_STATIC_SCRATCH_BYTES) return GQA_ERR_LIMIT;
   // The array still holds the previous call's bytes: deques, tickets and status must start
-  // at zero (everything in front of the partial slots).
-  e = cudaMemsetAsync(base, 0, w.lse_off, static_cast<cudaStream_t>(args->stream));
-  if (e != cudaSuccess) return (int)e;
+  // at zero (everything in front of the partial slots).  run_decode clears them on the stream
+  // after its own checks, so a call that is rejected leaves the array - which a launch in
+  // flight on another stream may be using - untouched.
   gqa_decode_args_t a = *args;
   a.workspace = base;
   a.workspace_bytes = GQA_STATIC_SCRATCH_BYTES;
-  return run_decode(&a, false, false);
+  return run_decode(&a, false, false, nullptr, /*clear_control=*/true);
 }
 
 int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num_parts,
@@ -725,7 +713,7 @@ size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim) 
 int gqa_exchange_merge(const float* local_o, const float* local_lse, void* const* peer_bufs,
                        int32_t rank, int32_t world, uint32_t epoch, int64_t rows,
                        int32_t head_dim, void* out, int32_t out_dtype, float* out_f32,
-                       float* out_lse, int32_t* status, void* stream) {
+                       float* out_lse, int32_t* status, uint64_t wait_limit_ns, void* stream) {
   if (!local_o || !local_lse || !peer_bufs || world <= 0 || world > kExchangeThreads ||
       rank < 0 || rank >= world || epoch == 0 || rows <= 0 || head_dim <= 0 || head_dim % 4 ||
       (!out && !out_f32))
@@ -746,6 +734,7 @@ int gqa_exchange_merge(const float* local_o, const float* local_lse, void* const
   p.out_f32 = out_f32;
   p.out_lse = out_lse;
   p.status = status;
+  p.wait_limit_ns = wait_limit_ns ? wait_limit_ns : kDefaultWaitLimitNs;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (out_dtype == GQA_DTYPE_FP16)
     exchange_merge_kernel<__half><<<world, kExchangeThreads, 0, st>>>(p);

@@ -29,6 +29,7 @@ constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kerne
 constexpr int kMaxStages = 8;
 constexpr int kMaxPeers = 8;  // GPUs of one NVLink domain that can gather head-sharded outputs
 constexpr int kDescRing = 32;  // tile descriptors kept in shared memory (>= 4 * kMaxStages)
+constexpr int kTimestampWords = 6;  // diagnostics words per CTA (DecodeParams::timestamps)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -65,10 +66,15 @@ struct DecodeParams {
   int no_merge;         // 1: every segment is written as a partial and nothing is merged
   int num_stages;
   int num_slots;        // partial slots the workspace holds
-  unsigned long long* timestamps;  // optional diagnostics: per CTA {start, first tile landed, end} in ns;
-                                   // builds with GQA_PROFILE_WAITS append, after those 3 * grid words,
+  unsigned long long* timestamps;  // optional diagnostics: kTimestampWords per CTA, %globaltimer ns:
+                                   // {prologue done, first load issued, first tile landed, start of
+                                   // the last segment's epilogue, end, 0}; builds with
+                                   // GQA_PROFILE_WAITS append, after those words of the whole grid,
                                    // per CTA {producer wait cycles, producer cycles, tiles posted,
                                    // consumer warp 0 wait-for-data cycles, consumer cycles}
+  unsigned long long wait_limit_ns;  // every bounded wait gives up after this long
+  int pdl;                  // 1: launched with programmatic stream serialization - the previous
+                            // kernel of the stream may still be running until griddep_wait()
   // paged K/V (sched.layout >= kLayoutPagedHnd)
   const int* block_table;   // [batch, table_stride] page numbers
   int page_size;            // rows per page
@@ -269,8 +275,7 @@ struct Kv16Traits {
   static constexpr int kMoStride = D + 8;  // floats per merge row; +8 keeps float2 stores conflict-free
   // float index of (merge row, column) inside a warp's block of merge rows
   __device__ static __forceinline__ int mo_index(int row, int col) { return row * kMoStride + col; }
-  // partials merged per L2 round trip (24 would save 2 us on single-sequence launches but
-  // costs the streaming loop 1.5 % through register pressure)
+  // partials the inline merge takes; groups with more go through merge_group_wide
   static constexpr int kMergeBatch = 8;
   struct Extra {};
   __device__ static __forceinline__ void begin_segment(Extra&, const DecodeParams&, int, int) {}
@@ -353,33 +358,87 @@ __device__ __forceinline__ void store_final_lse(const DecodeParams& prm, long lo
   if (prm.out_lse) prm.out_lse[out_row] = lse;
 }
 
-// `lse_smem` (capacity `lse_cap` floats) stages the group's n*G log-sum-exps so that the
-// weights come from shared memory; partial outputs are fetched kBatch at a time so that
-// the L2 round trips overlap instead of forming one dependent chain per partial (up to
-// kBatch partials need a single round trip).
-// All `nthreads` threads of named barrier 1 must call it together.
-template <typename Q, int D, int kBatch = 8>
-__device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_slot, int n,
-                                            long long out_row0, int tid, int nthreads,
-                                            float* lse_smem, int lse_cap) {
+// One (row, 4-column slice) of a merged group from its partial values: weights
+// e^(lse_i - max), normalised sum, final store.
+template <typename Q, int D, int N>
+__device__ __forceinline__ void merge_finish(const DecodeParams& prm, long long out_row, int d4,
+                                             const float4 (&o)[N], const float (&l)[N]) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < N; ++u) mx = fmaxf(mx, l[u]);
+  const float ms = (mx == -INFINITY) ? 0.f : mx;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float wsum = 0.f;
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    const float w = fast_exp2((l[u] - ms) * kLog2e);
+    acc.x += w * o[u].x;
+    acc.y += w * o[u].y;
+    acc.z += w * o[u].z;
+    acc.w += w * o[u].w;
+    wsum += w;
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  acc.x *= inv;
+  acc.y *= inv;
+  acc.z *= inv;
+  acc.w *= inv;
+  store_final<Q, D>(prm, out_row, d4, acc);
+  if (d4 == 0)
+    store_final_lse<D>(prm, out_row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+}
+
+// Up to kBatch partials: every thread fetches the handful of log-sum-exps it needs together
+// with the outputs, so the whole merge costs one L2 round trip.
+template <typename Q, int D, int kBatch>
+__device__ __forceinline__ void merge_small(const DecodeParams& prm, int first_slot, int n,
+                                            long long out_row0, int tid, int nthreads) {
   const int G = prm.group;
   constexpr int D4 = D / 4;
   const float* lse_g = prm.part_lse + (size_t)first_slot * G;  // [n, G], contiguous slots
-  // few partials: every thread fetches the handful of LSEs it needs together with the
-  // outputs (one round trip); many partials: stage the LSEs in shared memory first
-  const bool staged = n > kBatch && n * G <= lse_cap;
-  if (staged) {
-    for (int i = tid; i < n * G; i += nthreads) lse_smem[i] = ld_cg_f32(lse_g + i);
-    bar_sync(1, nthreads);
-  }
   for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
-    const float4* o_g = reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
-    if (n <= kBatch) {
-      float4 o[kBatch];
-      float l[kBatch];
+    const float4* o_g =
+        reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
+    float4 o[kBatch];
+    float l[kBatch];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
+      if (u < n) {
+        l[u] = ld_cg_f32(lse_g + (size_t)u * G + row);
+        o[u] = ld_cg_f32x4(o_g + (size_t)u * G * D4);
+      } else {
+        l[u] = -INFINITY;
+        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    merge_finish<Q, D, kBatch>(prm, out_row0 + row, d4, o, l);
+  }
+}
+
+// Many partials (a single long sequence spreads every group over about twenty CTAs): the
+// same single round trip with kMergeWide partials per thread.  Kept out of line so that its
+// hundred-odd live registers do not weigh on the register allocation of the streaming loop;
+// the launch parameters are reached through their address in the parameter space.
+// More than kMergeWide partials: a first pass finds the row's largest log-sum-exp, then the
+// outputs come kMergeWide at a time.
+constexpr int kMergeWide = 24;
+template <typename Q, int D>
+__device__ __noinline__ void merge_group_wide(const DecodeParams* __restrict__ prmp, int first_slot,
+                                              int n, long long out_row0, int tid, int nthreads) {
+  const DecodeParams& prm = *prmp;
+  const int G = prm.group;
+  constexpr int D4 = D / 4;
+  const float* lse_g = prm.part_lse + (size_t)first_slot * G;
+  for (int idx = tid; idx < G * D4; idx += nthreads) {
+    const int row = idx / D4, d4 = idx % D4;
+    const float4* o_g =
+        reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
+    if (n <= kMergeWide) {
+      float4 o[kMergeWide];
+      float l[kMergeWide];
+#pragma unroll
+      for (int u = 0; u < kMergeWide; ++u) {
         if (u < n) {
           l[u] = ld_cg_f32(lse_g + (size_t)u * G + row);
           o[u] = ld_cg_f32x4(o_g + (size_t)u * G * D4);
@@ -388,57 +447,37 @@ __device__ __forceinline__ void merge_group(const DecodeParams& prm, int first_s
           o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) mx = fmaxf(mx, l[u]);
-      const float ms = (mx == -INFINITY) ? 0.f : mx;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      float wsum = 0.f;
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const float w = fast_exp2((l[u] - ms) * kLog2e);
-        acc.x += w * o[u].x;
-        acc.y += w * o[u].y;
-        acc.z += w * o[u].z;
-        acc.w += w * o[u].w;
-        wsum += w;
-      }
-      const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-      acc.x *= inv;
-      acc.y *= inv;
-      acc.z *= inv;
-      acc.w *= inv;
-      store_final<Q, D>(prm, out_row0 + row, d4, acc);
-      if (d4 == 0)
-        store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+      merge_finish<Q, D, kMergeWide>(prm, out_row0 + row, d4, o, l);
       continue;
     }
     float mx = -INFINITY;
-    if (staged) {
-      for (int p = 0; p < n; ++p) mx = fmaxf(mx, lse_smem[p * G + row]);
-    } else {
-      for (int p = 0; p < n; ++p) mx = fmaxf(mx, ld_cg_f32(lse_g + (size_t)p * G + row));
+    for (int p0 = 0; p0 < n; p0 += 32) {
+      float l[32];
+#pragma unroll
+      for (int u = 0; u < 32; ++u)
+        l[u] = p0 + u < n ? ld_cg_f32(lse_g + (size_t)(p0 + u) * G + row) : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 32; ++u) mx = fmaxf(mx, l[u]);
     }
     const float ms = (mx == -INFINITY) ? 0.f : mx;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    for (int p0 = 0; p0 < n; p0 += kBatch) {
-      float4 o[kBatch];
-      float w[kBatch];
+    for (int p0 = 0; p0 < n; p0 += kMergeWide) {
+      float4 o[kMergeWide];
+      float w[kMergeWide];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
+      for (int u = 0; u < kMergeWide; ++u) {
         const int p = p0 + u;
         if (p < n) {
           o[u] = ld_cg_f32x4(o_g + (size_t)p * G * D4);
-          const float l = staged ? lse_smem[p * G + row] : ld_cg_f32(lse_g + (size_t)p * G + row);
-          w[u] = fast_exp2((l - ms) * kLog2e);
+          w[u] = fast_exp2((ld_cg_f32(lse_g + (size_t)p * G + row) - ms) * kLog2e);
         } else {
           o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
           w[u] = 0.f;
         }
       }
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
+      for (int u = 0; u < kMergeWide; ++u) {
         acc.x += w[u] * o[u].x;
         acc.y += w[u] * o[u].y;
         acc.z += w[u] * o[u].z;
@@ -494,6 +533,7 @@ struct Producer {
   uint32_t stg, par;  // stage of tile `it` and the parity of its use: it % nst, (it / nst) & 1
   int nst, lane;
   bool dead;
+  bool wait_grid;  // the previous kernel of the stream has not been waited for yet
   // paged layouts: 32 consecutive block-table entries of one sequence, one per lane
   int pg_seq, pg_base, pg_entry;
 #ifdef GQA_PROFILE_WAITS
@@ -508,12 +548,16 @@ struct Producer {
   // loads (or just signal when there is no data).  All lanes call it; lane 0 acts.
   __device__ __forceinline__ void post(const TileDesc& d, long long row) {
     if (dead) return;
+    if (wait_grid) {
+      griddep_wait();
+      wait_grid = false;
+    }
     const uint32_t s = stg, ph = par;
     int ok = 1;
 #ifdef GQA_PROFILE_WAITS
     const long long w0 = clock64();
 #endif
-    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
+    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, prm->wait_limit_ns) ? 1 : 0;
 #ifdef GQA_PROFILE_WAITS
     wait_cycles += clock64() - w0;
 #endif
@@ -542,6 +586,7 @@ struct Producer {
       } else {
         mbar_arrive(fb);
       }
+      if (it == 0 && prm->timestamps) prm->timestamps[kTimestampWords * blockIdx.x + 1] = global_timer_ns();
     }
     __syncwarp();
     step();
@@ -553,6 +598,10 @@ struct Producer {
   // mask those rows).  The block table is read 32 entries at a time, one per lane.
   __device__ __forceinline__ void post_paged(const TileDesc& d, int key0) {
     if (dead) return;
+    if (wait_grid) {
+      griddep_wait();
+      wait_grid = false;
+    }
     const uint32_t s = stg, ph = par;
     // (shifts instead of divisions: this runs once per tile on the producer's critical path)
     const int ps = prm->page_size, psh = prm->page_shift, bsh = prm->box_shift;
@@ -572,7 +621,7 @@ struct Producer {
     const int pidx = psh >= 0 ? key >> psh : key / ps;
     const int page = __shfl_sync(0xffffffffu, pg_entry, min(pidx - pg_base, 31));
     int ok = 1;
-    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u) ? 1 : 0;
+    if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, prm->wait_limit_ns) ? 1 : 0;
     if (!__shfl_sync(0xffffffffu, ok, 0)) {
       if (lane == 0) atomicOr(prm->status, kStatusWaitEmpty);
       dead = true;
@@ -705,7 +754,7 @@ struct ChunkSource {
 template <class Tr>
 __global__ void __launch_bounds__(BlockShape<Tr>::kThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-              const DecodeParams prm) {
+              const __grid_constant__ DecodeParams prm) {
   using Q = typename Tr::Q;
   constexpr int D = Tr::D;
   constexpr int TILE = Tr::TILE;
@@ -751,12 +800,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     tma_prefetch_desc(&tm_v);
   }
   __syncthreads();
-  if (prm.timestamps && tid == 0) prm.timestamps[3 * blockIdx.x] = global_timer_ns();
+  // Nothing above touched global memory.  Under programmatic dependent launch the next
+  // kernel of the stream may be scheduled from here on (its CTAs become resident as this
+  // grid's CTAs leave their SMs) and this kernel must wait for the previous one before it
+  // reads inputs that kernel may have written, or touches the workspace they share.
+  if (prm.pdl) griddep_launch_dependents();
+  if (prm.timestamps && tid == 0) prm.timestamps[kTimestampWords * blockIdx.x] = global_timer_ns();
 
   if (warp >= kConsumerWarps) {
     // ------------------------------------------------------------ producer warp
     if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp != kConsumerWarps) return;
+    // With uniform lengths and static ranges the schedule is pure arithmetic: it is worked
+    // out while the previous kernel drains, and the wait moves to the first load.
+    const bool wait_late = prm.pdl && !prm.sched.seq_lens && !prm.sched.steal;
+    if (prm.pdl && !wait_late) griddep_wait();
     Walker wk;
     wk.init_warp(prm.sched);
     Producer<Tr> pr;
@@ -775,6 +833,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     pr.nst = nst;
     pr.lane = lane;
     pr.dead = false;
+    pr.wait_grid = wait_late;
 #ifdef GQA_PROFILE_WAITS
     pr.wait_cycles = 0;
     const long long pc0 = clock64();
@@ -880,7 +939,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     pr.post(d, 0);
 #ifdef GQA_PROFILE_WAITS
     if (prm.timestamps && lane == 0) {
-      unsigned long long* ts = prm.timestamps + 3 * gridDim.x + 5 * blockIdx.x;
+      unsigned long long* ts = prm.timestamps + kTimestampWords * gridDim.x + 5 * blockIdx.x;
       ts[0] = (unsigned long long)pr.wait_cycles;
       ts[1] = (unsigned long long)(clock64() - pc0);
       ts[2] = pr.it;
@@ -891,6 +950,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   // -------------------------------------------------------------- consumers
   if (BlockShape<Tr>::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+  if (prm.pdl) griddep_wait();
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
   const bool dynamic = prm.sched.num_splits == 0 && prm.sched.steal;
@@ -927,7 +987,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (*sm_published <= (int)it) {
       const unsigned long long t0 = global_timer_ns();
       while (*sm_published <= (int)it) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > prm.wait_limit_ns) {
           ok = false;
           break;
         }
@@ -954,7 +1014,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #ifdef GQA_PROFILE_WAITS
     const long long cw0 = clock64();
 #endif
-    if (!mbar_wait(full0 + 8 * s, ph)) {
+    if (!mbar_wait(full0 + 8 * s, ph, prm.wait_limit_ns)) {
       // every consumer warp waits on the same barrier, so all of them give up together
       if (lane == 0) atomicOr(prm.status, kStatusWaitFull);
       break;
@@ -962,7 +1022,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #ifdef GQA_PROFILE_WAITS
     cons_wait += clock64() - cw0;
 #endif
-    if (prm.timestamps && tid == 0 && it == 0) prm.timestamps[3 * blockIdx.x + 1] = global_timer_ns();
+    if (prm.timestamps && tid == 0 && it == 0)
+      prm.timestamps[kTimestampWords * blockIdx.x + 2] = global_timer_ns();
     if (d.valid > 0) {
       ++seg_tiles;
       {
@@ -993,6 +1054,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
 
     // ---- end of a segment: combine the consumer warps' states ------------------------
+    if (prm.timestamps && tid == 0) prm.timestamps[kTimestampWords * blockIdx.x + 3] = global_timer_ns();
 #pragma unroll
     for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -1101,10 +1163,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
       bar_sync(1, kConsumerThreads);
       const int n = *sm_flag;
-      if (n > 0) {
-        merge_group<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads,
-                                           sm_o, kConsumerWarps * grows * kMoStride);
-      }
+      if (n > Tr::kMergeBatch)
+        merge_group_wide<Q, D>(&prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
+      else if (n > 0)
+        merge_small<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
     bar_sync(1, kConsumerThreads);
@@ -1112,7 +1174,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
 #ifdef GQA_PROFILE_WAITS
   if (prm.timestamps && tid == 0) {
-    unsigned long long* ts = prm.timestamps + 3 * gridDim.x + 5 * blockIdx.x;
+    unsigned long long* ts = prm.timestamps + kTimestampWords * gridDim.x + 5 * blockIdx.x;
     ts[3] = (unsigned long long)cons_wait;
     ts[4] = (unsigned long long)(clock64() - cc0);
   }
@@ -1146,7 +1208,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const unsigned* mine = prm.gather_flags[prm.gather_rank] + par * w + tid;
       const unsigned long long t0 = global_timer_ns();
       while (ld_acquire_sys(mine) != prm.gather_epoch) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > prm.wait_limit_ns) {
           atomicOr(prm.status, kStatusWaitExchange);
           arrived = 0;
           break;
@@ -1204,7 +1266,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
   }
   if (tid == 0) {
-    if (prm.timestamps) prm.timestamps[3 * blockIdx.x + 2] = global_timer_ns();
+    if (prm.timestamps) prm.timestamps[kTimestampWords * blockIdx.x + 4] = global_timer_ns();
     // work stealing only: the last CTA to finish leaves the chunk deques clean for the
     // next launch
     if (dynamic) {
@@ -1221,14 +1283,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 // the in-kernel merge is switched off.
 template <typename Q, int D>
 __global__ void __launch_bounds__(kMergeThreads)
-merge_groups_kernel(const DecodeParams prm) {
+merge_groups_kernel(const __grid_constant__ DecodeParams prm) {
   const long long g = blockIdx.x;
   const int2 info = prm.group_info[g];
   if (info.y <= 1) return;  // written directly by the decode kernel
-  __shared__ float lse_stage[4096];
   const long long b = g / prm.sched.num_kv_heads, h = g % prm.sched.num_kv_heads;
-  merge_group<Q, D>(prm, info.x, info.y, b * prm.num_q_heads + h * prm.group, threadIdx.x,
-                    kMergeThreads, lse_stage, 4096);
+  const long long out_row0 = b * prm.num_q_heads + h * prm.group;
+  if (info.y <= 8) merge_small<Q, D, 8>(prm, info.x, info.y, out_row0, threadIdx.x, kMergeThreads);
+  else merge_group_wide<Q, D>(&prm, info.x, info.y, out_row0, threadIdx.x, kMergeThreads);
 }
 
 }  // namespace gqa

@@ -35,6 +35,7 @@ struct ExchangeParams {
   float* out_f32;          // optional
   float* out_lse;          // optional
   int* status;             // optional device word: |= kStatusWaitExchange on expiry
+  unsigned long long wait_limit_ns;  // bound on the wait for the peers' flags
 };
 constexpr int kExchangeThreads = 256;
 
@@ -84,7 +85,7 @@ exchange_merge_kernel(const ExchangeParams p) {
     if (tid < p.world) {
       const unsigned long long t0 = global_timer_ns();
       while (ld_acquire_sys(flags + tid) != p.epoch) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > p.wait_limit_ns) {
           timed_out = 1;
           break;
         }

@@ -39,24 +39,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: every spin in these kernels gives up after kWaitLimitNs of wall time
-// (read from the global nanosecond timer), so a lost signal turns into an error code
-// instead of a hung GPU.  Legitimate waits last microseconds.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+// Bounded wait: every spin in these kernels gives up after a limit of wall time (read from
+// the global nanosecond timer), so a lost signal turns into an error code instead of a hung
+// GPU.  Legitimate waits last microseconds.  The limit is a launch argument; this is its
+// default.
+constexpr unsigned long long kDefaultWaitLimitNs = 2000000000ull;  // 2 s
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with programmatic stream serialization may start while the previous
+// kernel of the stream is still running.  griddep_wait() returns once that kernel has
+// completed and its writes are visible; griddep_launch_dependents() lets the next kernel's
+// CTAs be scheduled as soon as every CTA of this grid has called it (or exited).  Both are
+// no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMA

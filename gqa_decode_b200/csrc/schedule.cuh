@@ -41,11 +41,6 @@
 
 namespace gqa {
 
-// (The compiler's 64-bit division already takes a short path for 32-bit operands; a manual
-// 32-bit special case measured slower.)
-GQA_HD long long fast_div(long long a, long long b) { return a / b; }
-GQA_HD long long fast_mod(long long a, long long b) { return a % b; }
-
 enum KvLayout : int {
   kLayoutPadded = 0,  // K/V [batch, Hkv, max_seq, D]: head slab of (b,h) starts at row (b*Hkv+h)*max_seq
   kLayoutPacked = 1,  // K/V [sum_b Hkv*len_b, D]: sequence b holds [Hkv, len_b, D] after all earlier sequences
@@ -131,25 +126,25 @@ struct Walker {
       return;
     }
     const long long c = p.chunk_tiles > 0 ? p.chunk_tiles : 1;
-    n_chunks = fast_div(total + c - 1, c);
+    n_chunks = (total + c - 1) / c;
     parts = n_chunks < p.num_ctas ? n_chunks : p.num_ctas;
   }
   GQA_HD long long chunk_tiles() const { return p.chunk_tiles > 0 ? p.chunk_tiles : 1; }
   // chunk (balanced) or unit (explicit) range owned by CTA c
   GQA_HD void cta_range(int c, long long& q0, long long& q1) const {
     if (p.num_splits > 0) {
-      q0 = fast_div(c * total, p.num_ctas);
-      q1 = fast_div((c + 1) * total, p.num_ctas);
+      q0 = (c * total) / p.num_ctas;
+      q1 = ((c + 1) * total) / p.num_ctas;
     } else if (c < parts) {
-      q0 = fast_div(c * n_chunks, parts);
-      q1 = fast_div((c + 1) * n_chunks, parts);
+      q0 = (c * n_chunks) / parts;
+      q1 = ((c + 1) * n_chunks) / parts;
     } else {
       q0 = q1 = 0;
     }
   }
   // owner of chunk q: largest c with floor(c*M/P) <= q (P <= M: every owner has chunks)
   GQA_HD long long cta_of_chunk(long long q) const {
-    return fast_div((q + 1) * parts - 1, n_chunks);
+    return ((q + 1) * parts - 1) / n_chunks;
   }
   GQA_HD void chunk_tile_range(long long q, long long& t0, long long& t1) const {
     t0 = q * chunk_tiles();
@@ -167,15 +162,15 @@ struct Walker {
   // no partial)
   GQA_HD long long group_first_tile_unit() const { return tiles_before_group + overhead(); }
   GQA_HD int group_first_slot() const {
-    return (int)(fast_div(group_first_tile_unit(), chunk_tiles()) + group_index());
+    return (int)(group_first_tile_unit() / chunk_tiles() + group_index());
   }
   GQA_HD int group_static_parts() const {
     const long long c = chunk_tiles();
-    return (int)(cta_of_chunk(fast_div(group_first_tile_unit() + ntg - 1, c)) -
-                 cta_of_chunk(fast_div(group_first_tile_unit(), c)) + 1);
+    return (int)(cta_of_chunk((group_first_tile_unit() + ntg - 1) / c) -
+                 cta_of_chunk(group_first_tile_unit() / c) + 1);
   }
   GQA_HD int group_static_index(int cta) const {
-    return (int)(cta - cta_of_chunk(fast_div(group_first_tile_unit(), chunk_tiles())));
+    return (int)(cta - cta_of_chunk(group_first_tile_unit() / chunk_tiles()));
   }
 
   // ---- positioning on unit t0 of the line (balanced) ---------------------------------
@@ -190,8 +185,8 @@ struct Walker {
     ntg = tiles_of(len);
     const int ung = ntg + overhead();
     const long long off = t0 - s_tiles_before;
-    h = (int)fast_div(off, ung);
-    ui = (int)fast_mod(off, ung);
+    h = (int)(off / ung);
+    ui = (int)(off % ung);
     ti = ui - overhead();
     tiles_before_group = s_tiles_before + (long long)h * ung;
   }

@@ -18,6 +18,21 @@ import torch
 import torch.distributed as dist
 
 
+def next_epoch(epoch: int) -> int:
+    """Epoch of the step after `epoch`.  Epochs are 32-bit, never 0 (0 means "no step yet" in
+    the flag words) and alternate in parity (the parity selects one of two buffer halves):
+    after 0xFFFFFFFF (odd) comes 2 (even), the same on every rank."""
+    return epoch + 1 if epoch < 0xFFFFFFFF else 2
+
+
+def _refuse_capture(what: str) -> None:
+    """Steps that hand data to other GPUs carry a fresh epoch (and buffer half) chosen on the
+    host each time; a CUDA graph would replay one epoch forever, find the flags already equal
+    to it and read stale peer data.  Such steps must run eagerly."""
+    if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+        raise RuntimeError(f"{what} cannot be captured in a CUDA graph: every step needs a new epoch")
+
+
 def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous, balanced [begin, end) of `total` items for `rank` (first ranks get the
     remainder)."""
@@ -58,7 +73,8 @@ class NvlinkExchange:
     ``rows`` (= batch * num_q_heads) and ``head_dim``.  Ranks must be separate processes on
     separate GPUs of one NVLink domain.  Plain peer loads/stores only (no multicast)."""
 
-    def __init__(self, rows: int, head_dim: int, device, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, rows: int, head_dim: int, device, group: Optional[dist.ProcessGroup] = None,
+                 wait_limit_ns: int = 0):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -78,6 +94,7 @@ class NvlinkExchange:
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        self.wait_limit_ns = int(wait_limit_ns)  # 0: the library's default of two seconds
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)  # every buffer is zeroed before anybody pushes into it
         self._ctypes = ctypes
@@ -93,13 +110,14 @@ class NvlinkExchange:
         if out is None:
             out = torch.empty(self.rows, self.head_dim, dtype=out_dtype, device=self.device)
         f32 = out.dtype == torch.float32
-        self.epoch += 1
+        _refuse_capture("NvlinkExchange.merge")
+        self.epoch = next_epoch(self.epoch)
         code = {torch.bfloat16: n.DTYPE_BF16, torch.float16: n.DTYPE_FP16}.get(out.dtype, 0)
         n.check(
             self._lib.gqa_exchange_merge(
                 o32.data_ptr(), lse.data_ptr(), self.handle.buffer_ptrs_dev, self.rank, self.world,
                 self.epoch, self.rows, self.head_dim, None if f32 else out.data_ptr(), code,
-                out.data_ptr() if f32 else None, None, self.status.data_ptr(),
+                out.data_ptr() if f32 else None, None, self.status.data_ptr(), self.wait_limit_ns,
                 torch.cuda.current_stream(self.device).cuda_stream),
             "gqa_exchange_merge")
         return out
@@ -159,7 +177,8 @@ class HeadGather:
     def _next(self, g):
         """Advance to the next step: bump the epoch and point `g` at that parity's buffers."""
         ctypes = self._ctypes
-        self.epoch += 1
+        _refuse_capture("HeadGather")
+        self.epoch = next_epoch(self.epoch)
         par = self.epoch & 1
         g.peer_out = ctypes.cast(self._peer_out[par], ctypes.POINTER(ctypes.c_void_p))
         g.peer_flags = ctypes.cast(self._peer_flags, ctypes.POINTER(ctypes.c_void_p))
@@ -174,8 +193,9 @@ class HeadGather:
         from .gqa_decode import plan_decode
 
         g = self._native.GatherArgs()
+        before = self.epoch
         self._next(g)
-        self.epoch -= 1  # nothing ran yet
+        self.epoch = before  # nothing ran yet
         inner = plan_decode(q_local, k_local, v_local, seq_lens, _gather=g, **kw)
 
         def run():
@@ -183,6 +203,7 @@ class HeadGather:
             inner.run()
             return view
 
+        run.status = inner.status  # synchronise and read the step's status word
         return run
 
     def decode(self, q_local, k_local, v_local, seq_lens=None, **kw) -> torch.Tensor:
@@ -247,7 +268,8 @@ class FusedSequenceExchange:
 
     def _next(self, g):
         ctypes = self._ctypes
-        self.epoch += 1
+        _refuse_capture("FusedSequenceExchange")
+        self.epoch = next_epoch(self.epoch)
         g.peer_out = ctypes.cast(self._peer_recv, ctypes.POINTER(ctypes.c_void_p))
         g.peer_flags = ctypes.cast(self._peer_flags, ctypes.POINTER(ctypes.c_void_p))
         g.world, g.rank, g.epoch = self.world, self.rank, self.epoch
@@ -271,14 +293,16 @@ class FusedSequenceExchange:
         from .gqa_decode import plan_decode
 
         g = self._native.GatherArgs()
+        before = self.epoch
         self._next(g)
-        self.epoch -= 1  # nothing ran yet
+        self.epoch = before  # nothing ran yet
         inner = plan_decode(q, k_shard, v_shard, seq_lens_shard, _gather=g, **kw)
 
         def run():
             self._next(g)
             return inner.run()
 
+        run.status = inner.status  # synchronise and read the step's status word
         return run
 
 

@@ -10,9 +10,10 @@ memory and streams only.
 from __future__ import annotations
 
 import ctypes
-import math
+import functools
+import weakref
 from dataclasses import dataclass
-from typing import Optional, Sequence
+from typing import Optional
 
 import torch
 
@@ -108,7 +109,30 @@ def reduce_partials(partial_out, partial_max, partial_sum, num_q_heads, num_spli
 # ---------------------------------------------------------------------------
 
 _DTYPE_CODE = {torch.bfloat16: _native.DTYPE_BF16, torch.float16: _native.DTYPE_FP16}
-_workspaces: dict = {}
+
+# The C library keeps no record of workspaces; this layer owns them and knows what they last
+# held.  A workspace's control words must be zero at launch, kernels leave them zero, and
+# their extent depends on the launch geometry: the "geometry key" below is that extent plus
+# the workspace size.  A launch whose key differs from the workspace's previous one, or whose
+# workspace has unknown contents, carries GQA_FLAG_CLEAR_WORKSPACE.
+_workspaces: dict = {}                       # (device type, index) -> [tensor, geometry key]
+_caller_workspaces = weakref.WeakKeyDictionary()  # caller-owned tensor -> geometry key
+
+
+@functools.lru_cache(maxsize=256)
+def _workspace_sizes(batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, device_index):
+    """(bytes needed, extent of the control words) for a launch geometry on a device."""
+    lib = _native.load()
+    need, ctrl = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    _native.check(
+        lib.gqa_decode_workspace_bytes(
+            batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, ctypes.byref(need)),
+        "gqa_decode_workspace_bytes")
+    _native.check(
+        lib.gqa_decode_workspace_control_bytes(
+            batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, ctypes.byref(ctrl)),
+        "gqa_decode_workspace_control_bytes")
+    return need.value, ctrl.value
 
 
 def workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_splits=0, num_ctas=0) -> int:
@@ -120,30 +144,74 @@ def workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_splits=0, nu
     return n.value
 
 
+def _device_key(device: torch.device):
+    return (device.type, device.index if device.index is not None else torch.cuda.current_device())
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """A zero-initialised scratch tensor per device, grown on demand and reused by
-    every call on that device (calls that overlap on different streams must pass their
-    own ``workspace=``)."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    every eager call on that device (calls that overlap on different streams must pass
+    their own ``workspace=``)."""
+    key = _device_key(device)
+    entry = _workspaces.get(key)
+    if entry is None or entry[0].numel() < nbytes:
+        entry = [torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device), None]
+        _workspaces[key] = entry
+    return entry[0]
 
 
-def read_status(workspace: Optional[torch.Tensor] = None, device=None) -> int:
+def _needs_clear(ws: torch.Tensor, device: torch.device, geometry) -> bool:
+    """Record that `ws` is about to serve a launch of `geometry`; True if its control words
+    must be cleared first (another geometry used it last, or its contents are unknown)."""
+    entry = _workspaces.get(_device_key(device))
+    if entry is not None and entry[0] is ws:
+        clear = entry[1] is not None and entry[1] != geometry  # None: still all zeros
+        entry[1] = geometry
+        return clear
+    clear = _caller_workspaces.get(ws) != geometry
+    _caller_workspaces[ws] = geometry
+    return clear
+
+
+def reset_workspace(workspace: Optional[torch.Tensor] = None, device=None) -> None:
+    """Zero a workspace (default: the shared one of the device) on the current stream.  Needed
+    after a launch that reported a non-zero status, whose tickets may be left half counted."""
+    if workspace is None:
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        entry = _workspaces.get(_device_key(dev))
+        if entry is None:
+            return
+        workspace, entry[1] = entry[0], None
+    else:
+        _caller_workspaces.pop(workspace, None)
+    with torch.cuda.device(workspace.device):
+        _native.check(
+            _native.load().gqa_decode_workspace_reset(
+                workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                torch.cuda.current_stream(workspace.device).cuda_stream),
+            "gqa_decode_workspace_reset")
+
+
+def read_status(workspace: Optional[torch.Tensor] = None, device=None, reset_on_error: bool = True) -> int:
     """Synchronise and return the kernels' status word (0 = ok; non-zero = a bounded
-    wait inside a kernel expired and the result of that call is invalid)."""
+    wait inside a kernel expired and the result of that call is invalid).  A workspace that
+    reports an error is zeroed again (``reset_on_error``) so that the next launch on it starts
+    from clean tickets."""
     if workspace is None:
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         workspace = _workspace(dev, 512)
+        shared = True
+    else:
+        shared = False
     st = ctypes.c_int32(0)
-    _native.check(
-        _native.load().gqa_decode_read_status(
-            workspace.data_ptr(), torch.cuda.current_stream(workspace.device).cuda_stream,
-            ctypes.byref(st)),
-        "gqa_decode_read_status")
+    with torch.cuda.device(workspace.device):
+        _native.check(
+            _native.load().gqa_decode_read_status(
+                workspace.data_ptr(), torch.cuda.current_stream(workspace.device).cuda_stream,
+                ctypes.byref(st)),
+            "gqa_decode_read_status")
+    if st.value and reset_on_error:
+        reset_workspace(None if shared else workspace, workspace.device)
     return st.value
 
 
@@ -173,6 +241,9 @@ def gqa_decode_attention_batched(
     fp8_exact_v: bool = False,
     work_stealing: bool = False,
     block_table: Optional[torch.Tensor] = None,
+    dependent_launch: bool = False,
+    wait_limit_ns: int = 0,
+    _timestamps: Optional[torch.Tensor] = None,
     _entry: str = "auto",
     _no_merge: bool = False,
     _plan_only: bool = False,
@@ -203,6 +274,14 @@ def gqa_decode_attention_batched(
     fp8_exact_v: round every dequantised V element to the 16-bit type as
       ``dequantize_kv_fp8`` does (K always is); default applies the V scale to the fp32
       output instead, which is faster and differs only in that rounding.
+    dependent_launch: launch with programmatic stream serialization, so that the kernel's
+      prologue overlaps the end of the previous kernel on the stream (it waits for that kernel
+      before reading inputs); for back-to-back decode steps.
+    wait_limit_ns: bound on every wait inside the kernel (0 = two seconds); on expiry the
+      status word (:func:`read_status`) is non-zero and the outputs are invalid.
+    workspace: a caller-owned uint8 CUDA tensor of :func:`workspace_bytes` bytes instead of
+      the shared per-device one; this module remembers what it last held and clears its
+      control words when the launch geometry changes.
     Returns out ``[B, Hq, D]`` (q dtype), plus float32 output and/or natural-log LSE
     ``[B, Hq]`` when asked.  A sequence of length 0 yields zeros and LSE = -inf.
     """
@@ -292,10 +371,20 @@ def gqa_decode_attention_batched(
         raise ValueError("num_splits must be positive")
 
     dev = q.device
-    need = workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas)
-    ws = workspace if workspace is not None else _workspace(dev, need)
-    if ws.numel() * ws.element_size() < need:
+    need, ctrl = _workspace_sizes(batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas,
+                                  _device_key(dev)[1])
+    if workspace is not None:
+        ws = workspace
+    elif _plan_only:
+        # a plan owns its workspace: fixed geometry, zero from the start, never needs clearing,
+        # and nothing another launch does can disturb a captured graph that replays it
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    else:
+        ws = _workspace(dev, need)
+    ws_bytes = ws.numel() * ws.element_size()
+    if ws_bytes < need:
         raise ValueError(f"workspace too small: need {need} bytes")
+    clear = (workspace is not None or not _plan_only) and _needs_clear(ws, dev, (ctrl, ws_bytes))
     if _gather is not None and _gather.mode == _native.GATHER_HEADS:
         out = None  # final rows go to the gathered buffers of every rank (distributed.HeadGather)
     elif out is None:
@@ -320,9 +409,13 @@ def gqa_decode_attention_batched(
     a.flags = (_native.FLAG_SEPARATE_MERGE if separate_merge else 0) | (
         _native.FLAG_NO_MERGE if _no_merge else 0) | (
         _native.FLAG_FP8_EXACT_V if fp8_exact_v else 0) | (
-        _native.FLAG_WORK_STEALING if work_stealing else 0)
+        _native.FLAG_WORK_STEALING if work_stealing else 0) | (
+        _native.FLAG_CLEAR_WORKSPACE if clear else 0) | (
+        _native.FLAG_DEPENDENT_LAUNCH if dependent_launch else 0)
+    a.wait_limit_ns = int(wait_limit_ns)
+    a.debug_timestamps = _timestamps.data_ptr() if _timestamps is not None else None
     a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws_bytes
     a.stream = torch.cuda.current_stream(dev).cuda_stream
     if code_layout >= _native.LAYOUT_PAGED_HND:
         a.block_table = block_table.data_ptr()
@@ -341,8 +434,8 @@ def gqa_decode_attention_batched(
     result = (out, *extras) if extras else out
     if _plan_only:
         keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse, block_table,
-                _gather)
-        return DecodePlan(fn, a, dev, result, keep)
+                _gather, _timestamps)
+        return DecodePlan(fn, a, dev, result, keep, ws)
     with torch.cuda.device(dev):
         _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")
     return result
@@ -353,18 +446,29 @@ class DecodePlan:
     encodes and one kernel launch) on the current stream of the plan's device, with no
     Python-side checks or allocations.  The tensors given to :func:`plan_decode` are
     read and written in place on every run, so a serving loop updates K/V/``seq_lens``
-    storage and calls ``run()`` again.  The stream is re-read on each run."""
+    storage and calls ``run()`` again.  The stream is re-read on each run.  Unless the caller
+    passed ``workspace=``, the plan has a workspace of its own (``plan.workspace``), so plans
+    may be captured in CUDA graphs and replayed in any order with other launches in between;
+    ``status()`` reads its status word."""
 
-    def __init__(self, fn, args, device, result, keep):
+    def __init__(self, fn, args, device, result, keep, workspace):
         self._fn, self._args, self.device, self.result, self._keep = fn, args, device, result, keep
         self._ref = ctypes.byref(args)
+        self.workspace = workspace
 
     def run(self):
         self._args.stream = torch.cuda.current_stream(self.device).cuda_stream
         rc = self._fn(self._ref)
         if rc:
             _native.check(rc, "gqa_decode_attention")
+        # a caller-owned workspace of unknown contents is cleared by the first run only
+        self._args.flags &= ~_native.FLAG_CLEAR_WORKSPACE
         return self.result
+
+    def status(self) -> int:
+        """Synchronise and return the status word of the plan's workspace (0 = ok)."""
+        st = read_status(self.workspace, reset_on_error=True)
+        return st
 
 
 def plan_decode(q, k_cache, v_cache, seq_lens=None, **kw) -> DecodePlan:

@@ -49,6 +49,15 @@ extern "C" {
 #define GQA_FLAG_FP8_EXACT_V 4    /* E4M3: round every dequantised V element to the 16-bit type like
                                      dequantize_kv_fp8 (gqa_decode/fp8_utils.py:54-55) instead of
                                      applying the V scale once to the fp32 output (default, faster) */
+#define GQA_FLAG_CLEAR_WORKSPACE 16 /* zero the workspace's control words (one small memset node on the
+                                     stream, after the arguments have been checked) before the
+                                     launch: for a workspace whose contents are unknown, or that
+                                     last served a launch of another geometry */
+#define GQA_FLAG_DEPENDENT_LAUNCH 32 /* launch with programmatic stream serialization: the kernel's
+                                     prologue (and, for uniform lengths, its scheduling) overlaps the
+                                     end of the previous kernel on the stream; it waits for that
+                                     kernel before it reads any input or touches the workspace.
+                                     Hides the launch gap between back-to-back steps */
 
 /* errors */
 #define GQA_ERR_ARG (-1)       /* null pointer, non-positive size, misaligned pointer */
@@ -93,12 +102,38 @@ typedef struct gqa_decode_args {
   const int32_t* block_table;  /* paged layouts: device [batch, block_table_stride] page numbers */
   int32_t page_size;           /* paged layouts: rows per page */
   int32_t block_table_stride;  /* paged layouts: table entries per sequence */
+  uint64_t wait_limit_ns;      /* bound on every wait inside the kernel (a tile that never lands,
+                                  a peer GPU's flag); on expiry a status bit is set and the
+                                  kernel returns.  0: two seconds */
+  uint64_t* debug_timestamps;  /* optional diagnostics: device buffer of 6 * num_ctas uint64; per
+                                  CTA {prologue done, first load issued, first tile landed, start
+                                  of the last segment's epilogue, end, unused} in %globaltimer ns */
 } gqa_decode_args_t;
 
-/* Bytes of device scratch a launch with these sizes needs (partials, tickets, status). */
+/*
+ * Bytes of device scratch a launch with these sizes needs (partials, tickets, status).
+ *
+ * Workspace contract.  The library keeps no record of workspaces.  The front of a
+ * workspace holds control words (status, tickets, counters) that must be ZERO when a launch
+ * starts; kernels leave them zero when they finish with status 0.  How far the control
+ * words reach depends on the launch geometry (gqa_decode_workspace_control_bytes), and
+ * partial results of one geometry may lie where another geometry keeps control words.  So:
+ * zero a workspace when it is created (gqa_decode_workspace_reset), and set
+ * GQA_FLAG_CLEAR_WORKSPACE (or call gqa_decode_workspace_reset) on the first launch after
+ * the geometry - batch, head counts, head_dim, num_splits, num_ctas, workspace_bytes -
+ * changed and after a launch that reported a non-zero status.  A workspace serves one
+ * launch at a time: launches that may overlap on the GPU need one each.
+ */
 int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                int32_t head_dim, int32_t num_splits, int32_t num_ctas,
                                size_t* bytes);
+
+/* Extent of the control words (bytes from the start of the workspace) for these sizes: what
+ * GQA_FLAG_CLEAR_WORKSPACE zeroes.  Two launches with equal extents on a workspace of equal
+ * size may follow each other without clearing. */
+int gqa_decode_workspace_control_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                       int32_t head_dim, int32_t num_splits, int32_t num_ctas,
+                                       size_t* bytes);
 
 /*
  * Byte offsets inside a workspace for explicit splits (num_splits = K > 0): offsets[0]
@@ -112,13 +147,14 @@ int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_
                                 int32_t head_dim, int32_t num_splits, int32_t num_ctas,
                                 size_t offsets[6]);
 
-/* Zero the ticket counters and the status word.  Call once after allocating a workspace
- * (kernels leave both clean) and after any launch that reported a non-zero status. */
+/* Zero a whole workspace on the stream.  Call once after allocating it and after any launch
+ * that reported a non-zero status. */
 int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Copy the status word back (synchronises the stream): 0 = ok, else OR of
  * 1 (consumer wait expired), 2 (producer wait expired), 4 (shared-memory misalignment),
- * 8 (a partial-slot index was out of range: the control words were not clean). */
+ * 8 (a partial-slot index was out of range: the control words were not clean),
+ * 16 (a peer GPU's flag never arrived: sequence exchange, head gather). */
 int gqa_decode_read_status(const void* workspace, void* stream, int32_t* status);
 
 /* bf16 / fp16 K and V.  Replaces gqa_decode_attention, gqa_decode/gqa_decode.py:672-762
@@ -159,8 +195,9 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
  *    stream capture is begun;
  *  - all calls on a device share the one array, which keeps whatever the previous call
  *    left: the entry clears the tickets and the status word on the stream before each
- *    launch, and two calls that overlap on the GPU (different streams, or different
- *    host threads) race on it - serialise them;
+ *    launch (after the arguments have been checked: a rejected call touches nothing), and
+ *    two calls that overlap on the GPU (different streams, or different host threads) race
+ *    on it - serialise them;
  *  - gqa_decode_read_status cannot be pointed at the array; a caller that wants the
  *    status word uses the workspace-taking entry instead.
  */
@@ -268,16 +305,17 @@ int gqa_quantize_append_fp8(const gqa_append_args_t* args);
  * DEVICE array of `world` pointers: the receive buffer of every rank as mapped into this
  * process (symmetric memory of gqa_exchange_buffer_bytes() bytes, zero-filled once when
  * created).  The kernel pushes the local partial to all peers with plain peer stores,
- * signals them, waits (bounded, 2 s) for all peers' partials and writes the merged
- * out / out_f32 / out_lse.  `epoch` must be > 0 and increase by one on every call, on all
- * ranks alike.  `status` (optional device word) gets bit 16 if a peer never arrived.
+ * signals them, waits (bounded by wait_limit_ns; 0 = two seconds) for all peers' partials and
+ * writes the merged out / out_f32 / out_lse.  `epoch` must be > 0 and increase by one on
+ * every call, on all ranks alike.  `status` (optional device word) gets bit 16 if a peer
+ * never arrived; the outputs are then left untouched.
  * All ranks must be separate processes on separate GPUs of one NVLink domain.
  */
 size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim);
 int gqa_exchange_merge(const float* local_o, const float* local_lse, void* const* peer_bufs,
                        int32_t rank, int32_t world, uint32_t epoch, int64_t rows,
                        int32_t head_dim, void* out, int32_t out_dtype, float* out_f32,
-                       float* out_lse, int32_t* status, void* stream);
+                       float* out_lse, int32_t* status, uint64_t wait_limit_ns, void* stream);
 
 /* One-wave split heuristic of the reference, gqa_decode/gqa_decode.py:80-102.
  * Returns the split count (>= 1) or a negative error. */
@@ -306,12 +344,6 @@ int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num
                              int32_t max_seq_len, int32_t tile_rows, int32_t num_ctas,
                              int32_t num_splits, int32_t kv_layout, int64_t* records,
                              int64_t capacity, int64_t* count, void* stream);
-
-/* Diagnostics: while a non-NULL device buffer of 3 * num_ctas uint64 is registered, every
- * decode launch of this process writes per CTA {start, first tile landed, end} as
- * %globaltimer nanoseconds into it (used to study launch ramp and tail).  NULL switches
- * it off.  Not thread-safe with concurrent launches. */
-int gqa_debug_set_timestamp_buffer(uint64_t* device_buffer);
 
 /* Library version string. */
 const char* gqa_decode_version(void);
