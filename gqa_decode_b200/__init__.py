@@ -12,6 +12,7 @@ from .gqa_decode import (
     read_status,
     reduce_partials,
     reference_gqa_decode,
+    reset_workspace,
     select_num_splits,
     workspace_bytes,
 )
@@ -28,6 +29,7 @@ __all__ = [
     "read_status",
     "reduce_partials",
     "reference_gqa_decode",
+    "reset_workspace",
     "select_num_splits",
     "workspace_bytes",
 ]

@@ -63,6 +63,8 @@ def test_static_scratch_entry_matches_workspace_entry():
         assert lib.gqa_decode_attention_static_scratch(
             ctypes.byref(_args(_native, q, k, v, sl, got, None, splits, fl))) == 0
         torch.cuda.synchronize()
+        # the workspace-taking launch reports its status word; the library's own array cannot be
+        # read from outside, so for the other launch the output comparison below is the evidence
         st = ctypes.c_int32(-1)
         assert lib.gqa_decode_read_status(ws.data_ptr(), None, ctypes.byref(st)) == 0 and st.value == 0
         assert not torch.isnan(got.float()).any()
@@ -99,3 +101,16 @@ def test_static_scratch_entry_rejects_oversized_launch():
     a = _args(_native, q, k, k, sl, out, None, num_splits=1400)
     assert lib.gqa_decode_attention_static_scratch(ctypes.byref(a)) == -5  # GQA_ERR_LIMIT
     assert lib.gqa_decode_attention_static_scratch(None) == -1
+    # requests the entry does not serve are turned away by the argument checks, before anything
+    # is enqueued that would touch the shared array: E4M3 caches, an unsupported head_dim
+    a = _args(_native, q, k, k, sl, out, None)
+    a.kv_dtype = _native.DTYPE_E4M3
+    assert lib.gqa_decode_attention_static_scratch(ctypes.byref(a)) == -2  # GQA_ERR_SHAPE
+    a = _args(_native, q, k, k, sl, out, None)
+    a.head_dim = 96
+    assert lib.gqa_decode_attention_static_scratch(ctypes.byref(a)) == -2
+    # and an accepted call right after them is still correct
+    a = _args(_native, q, k, k, sl, out, None)
+    assert lib.gqa_decode_attention_static_scratch(ctypes.byref(a)) == 0
+    torch.cuda.synchronize()
+    assert bool((out == 0).all())  # zero K and V: uniform weights over zero rows
