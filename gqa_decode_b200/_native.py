@@ -20,7 +20,8 @@ FLAG_FP8_EXACT_V = 4
 FLAG_WORK_STEALING = 8
 FLAG_CLEAR_WORKSPACE = 16
 FLAG_DEPENDENT_LAUNCH = 32
-TIMESTAMP_WORDS = 6  # uint64 words per CTA in DecodeArgs.debug_timestamps
+FLAG_TICKET_MERGE = 64
+TIMESTAMP_WORDS = 8  # uint64 words per CTA in DecodeArgs.debug_timestamps
 STATIC_SCRATCH_BYTES = 16 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {
@@ -78,8 +79,6 @@ SIGNATURES = {
     "gqa_decode_tile_rows": (ctypes.c_int, [c_int32, c_int32]),
     "gqa_decode_workspace_bytes": (
         ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
-    "gqa_decode_workspace_control_bytes": (
-        ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
     "gqa_decode_workspace_layout": (
         ctypes.c_int, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]),
     "gqa_decode_workspace_reset": (ctypes.c_int, [c_void_p, c_size_t, c_void_p]),
@@ -97,6 +96,7 @@ SIGNATURES = {
     "gqa_decode_attention_gather": (ctypes.c_int, [POINTER(DecodeArgs), POINTER(GatherArgs)]),
     "gqa_quantize_append_fp8": (ctypes.c_int, [POINTER(AppendArgs)]),
     "gqa_exchange_buffer_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
+    "gqa_sequence_exchange_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "gqa_exchange_merge": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_void_p, c_int32, c_int32, ctypes.c_uint32, c_int64, c_int32,

@@ -38,17 +38,27 @@ def needs_build() -> bool:
     return any(os.path.getmtime(s) > built for s in _sources())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/*.cu into lib/libgqa_decode_b200.so and return its path."""
+def build(force: bool = False, verbose: bool = False, defines=(), output: str = "") -> str:
+    """Compile csrc/*.cu into lib/libgqa_decode_b200.so and return its path.  `defines`
+    (macro definitions) together with `output` build a differently configured library
+    elsewhere, e.g. -DGQA_PROFILE_WAITS for the diagnostics counters; such a library is
+    selected at run time through the environment variable GQA_DECODE_B200_LIB."""
+    if output:
+        return _compile(output, verbose, defines)
     if not force and not needs_build():
         return LIB_PATH
+    return _compile(LIB_PATH, verbose, defines)
+
+
+def _compile(LIB_PATH: str, verbose: bool, defines) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: cannot build libgqa_decode_b200.so")
-    os.makedirs(LIB_DIR, exist_ok=True)
+    os.makedirs(os.path.dirname(os.path.abspath(LIB_PATH)), exist_ok=True)
     cus = [s for s in _sources() if s.endswith(".cu")]
     tmp = LIB_PATH + ".tmp"
-    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *cus, "-o", tmp]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *[f"-D{d}" for d in defines],
+           *cus, "-o", tmp]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
@@ -59,4 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    outs = [a[6:] for a in sys.argv[1:] if a.startswith("--out=")]
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, defines=defs,
+                output=outs[0] if outs else ""))

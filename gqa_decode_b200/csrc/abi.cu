@@ -180,10 +180,10 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, DecodePar
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// `clear_control`: zero the workspace's control words on the stream once every check has
-// passed (GQA_FLAG_CLEAR_WORKSPACE asks for the same).
+// `own_scratch`: the call runs on the library's own scratch array (completion tickets, control
+// words cleared on the stream once every check has passed).
 static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_balanced,
-                      const gqa_gather_args_t* gather = nullptr, bool clear_control = false) {
+                      const gqa_gather_args_t* gather = nullptr, bool own_scratch = false) {
   if (!a || !a->q || !a->k || !a->v || !a->workspace) return GQA_ERR_ARG;
   if ((!gather || gather->mode == GQA_GATHER_SEQUENCE) && !a->out && !a->out_f32) return GQA_ERR_ARG;
   if (gather) {
@@ -304,6 +304,12 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)D);
   prm.scale_log2 = scale * kLog2e;
   prm.fused_merge = fused ? 1 : 0;
+  // Partials that announce themselves need every contributor of a group to be resident (or
+  // finished) while the group's last CTA polls: guaranteed with at most one CTA per SM.
+  prm.polled = (fused && !prm.sched.steal && !own_scratch && !(a->flags & GQA_FLAG_TICKET_MERGE) &&
+                num_ctas <= sm_count_or(0))
+                   ? 1
+                   : 0;
   prm.no_merge = no_merge ? 1 : 0;
   prm.num_slots = (int)w.slots;
   prm.timestamps = reinterpret_cast<unsigned long long*>(a->debug_timestamps);
@@ -331,8 +337,9 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     prm.gather_rows = (long long)a->batch * a->num_q_heads;
   }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
-  if (clear_control || (a->flags & GQA_FLAG_CLEAR_WORKSPACE)) {
-    cudaError_t e = cudaMemsetAsync(a->workspace, 0, w.lse_off, st);
+  if (own_scratch || (a->flags & GQA_FLAG_CLEAR_WORKSPACE)) {
+    // control words always; the partial area too when the launch expects it to be zero
+    cudaError_t e = cudaMemsetAsync(a->workspace, 0, prm.polled ? w.total : w.lse_off, st);
     if (e != cudaSuccess) return (int)e;
   }
   const bool upper = G > 8;
@@ -507,19 +514,6 @@ int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_k
   return 0;
 }
 
-int gqa_decode_workspace_control_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
-                                       int32_t head_dim, int32_t num_splits, int32_t num_ctas,
-                                       size_t* bytes) {
-  if (!bytes || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
-      num_splits < 0 || num_ctas < 0 || num_q_heads % num_kv_heads)
-    return GQA_ERR_ARG;
-  const int ctas = num_ctas > 0 ? num_ctas : sm_count_or(1024);
-  // the control words end where the partial log-sum-exps begin, whatever the slot count
-  *bytes = layout_workspace((long long)batch * num_kv_heads, ctas, 0, num_q_heads / num_kv_heads,
-                            head_dim).lse_off;
-  return 0;
-}
-
 int gqa_decode_workspace_layout(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                 int32_t head_dim, int32_t num_splits, int32_t num_ctas,
                                 size_t offsets[6]) {
@@ -610,7 +604,7 @@ int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args) {
   gqa_decode_args_t a = *args;
   a.workspace = base;
   a.workspace_bytes = GQA_STATIC_SCRATCH_BYTES;
-  return run_decode(&a, false, false, nullptr, /*clear_control=*/true);
+  return run_decode(&a, false, false, nullptr, /*own_scratch=*/true);
 }
 
 int gqa_merge_partials(const float* o_parts, const float* lse_parts, int32_t num_parts,
@@ -703,6 +697,11 @@ int gqa_quantize_append_fp8(const gqa_append_args_t* a) {
   else
     append_quantize_kernel<__half><<<grid, a->head_dim / 4, 0, st>>>(p);
   return (int)cudaGetLastError();
+}
+
+size_t gqa_sequence_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim) {
+  if (world <= 0 || rows <= 0 || head_dim <= 0) return 0;
+  return (size_t)2 * world * sequence_exchange_slot_words(rows, head_dim) * sizeof(uint2);
 }
 
 size_t gqa_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t head_dim) {

@@ -29,7 +29,8 @@ constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kerne
 constexpr int kMaxStages = 8;
 constexpr int kMaxPeers = 8;  // GPUs of one NVLink domain that can gather head-sharded outputs
 constexpr int kDescRing = 32;  // tile descriptors kept in shared memory (>= 4 * kMaxStages)
-constexpr int kTimestampWords = 6;  // diagnostics words per CTA (DecodeParams::timestamps)
+constexpr int kTimestampWords = 8;  // diagnostics words per CTA (DecodeParams::timestamps)
+constexpr int kDeferCap = 4;  // group merges a CTA puts off until its streaming is over (one is the rule)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -40,6 +41,7 @@ enum StatusBits : int {
   kStatusSmemAlign = 4,   // shared memory base not 1024-byte aligned
   kStatusSlotRange = 8,   // a partial slot index fell outside the workspace (write skipped)
   kStatusWaitExchange = 16,  // a peer GPU's flag never arrived (sequence exchange, head gather)
+  kStatusWaitPartial = 32,   // a partial of a group never arrived at the CTA that merges the group
 };
 
 struct DecodeParams {
@@ -62,13 +64,19 @@ struct DecodeParams {
   int num_q_heads;
   int group;            // G = Hq / Hkv
   float scale_log2;     // softmax scale * log2(e)
-  int fused_merge;      // 1: the CTA that completes a group merges its partials in this launch
+  int fused_merge;      // 1: the partials of a group are merged inside this launch
+  int polled;           // fused merge, static schedule: 1 = partials announce themselves (a word that
+                        // is not zero has arrived; the partial area is all zero between launches
+                        // and writers turn +0 into -0) and the CTA that writes a group's last
+                        // partial polls for the others; 0 = completion tickets (atomics)
   int no_merge;         // 1: every segment is written as a partial and nothing is merged
   int num_stages;
   int num_slots;        // partial slots the workspace holds
   unsigned long long* timestamps;  // optional diagnostics: kTimestampWords per CTA, %globaltimer ns:
                                    // {prologue done, first load issued, first tile landed, start of
-                                   // the last segment's epilogue, end, 0}; builds with
+                                   // the last segment's epilogue, end, ticket drawn by the CTA's
+                                   // last merging segment (0: it merged nothing), SM id, tile
+                                   // descriptors consumed}; builds with
                                    // GQA_PROFILE_WAITS append, after those words of the whole grid,
                                    // per CTA {producer wait cycles, producer cycles, tiles posted,
                                    // consumer warp 0 wait-for-data cycles, consumer cycles}
@@ -89,10 +97,13 @@ struct DecodeParams {
   unsigned* gather_flags[kMaxPeers];  // every rank's [2 parities][world] flag words
   int gather_world, gather_rank;
   unsigned gather_epoch;
-  // gather_mode 1 (sequence sharding): gather_out[p] is rank p's receive area of floats,
-  // [2 parities][source rank][rows * D outputs, rows log-sum-exps]; every rank's normalised
-  // fp32 rows and LSEs are pushed there, and after the flags every CTA merges its share of
-  // the rows from the `world` partials now in local memory into out / out_f32 / out_lse
+  // gather_mode 1 (sequence sharding): gather_out[p] is rank p's receive area of 8-byte words
+  // {float value, epoch}: [2 parities][source rank][rows * D outputs, rows log-sum-exps (padded
+  // to an even count)].  Every rank's normalised fp32 rows and LSEs are pushed there as soon
+  // as they exist; a word is valid once its tag equals the step's epoch, so the data is its
+  // own arrival flag (no fence, no separate flag, no counter).  At the end of the kernel
+  // every CTA merges its share of the rows from the `world` partials into out / out_f32 /
+  // out_lse, waiting (bounded) for words that have not landed yet.
   int gather_mode;
   long long gather_rows;    // batch * Hq
 };
@@ -107,7 +118,12 @@ struct TileDesc {
   int slot;         // slot of this segment's partial, or -1: allocate at the end of the segment
   int n_parts;      // partials of the group if known in advance (static schedules), else 0
 };
-enum TileFlags : int { kTileFirst = 1, kTileLast = 2, kTileEnd = 4 };
+enum TileFlags : int {
+  kTileFirst = 1,
+  kTileLast = 2,
+  kTileEnd = 4,
+  kTileShared = 8,  // other CTAs contribute partials to this tile's group
+};
 
 __host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_stages, int mo_stride,
                                                     int group_rows, int consumer_warps) {
@@ -117,7 +133,7 @@ __host__ __device__ inline size_t decode_smem_bytes(int stage_bytes, int num_sta
   b += (size_t)consumer_warps * group_rows * 2 * sizeof(float);
   b += 2 * kMaxStages * sizeof(uint64_t);
   b += kDescRing * sizeof(TileDesc);
-  b += 64;
+  b += 128;  // flag words and the list of deferred merges (8 + 3 * kDeferCap ints)
   return b;
 }
 
@@ -312,16 +328,46 @@ struct Kv16Traits {
 // Merge `n` partials of one group (rows = G query heads) and write the result.
 // Executed by the 128 consumer threads of the CTA that completed the group.
 // ---------------------------------------------------------------------------
+// 8-byte words one source rank's partial occupies in a receive area of the sequence exchange
+// (rows * D outputs, then the rows' log-sum-exps padded to an even count so that every
+// source's block starts on a 16-byte boundary).
+__host__ __device__ inline size_t sequence_exchange_slot_words(long long rows, int D) {
+  return (size_t)rows * D + (size_t)((rows + 1) & ~1ll);
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.volatile.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
+  asm volatile("st.volatile.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 template <typename Q, int D>
 __device__ __forceinline__ void store_final(const DecodeParams& prm, long long out_row, int d4,
                                             float4 v) {
   if (prm.gather_world > 0 && prm.gather_mode == 1) {
-    // sequence shard: this rank's normalised fp32 row goes to every rank's receive area
-    const size_t slot = (size_t)prm.gather_rows * (D + 1);
+    // sequence shard: this rank's normalised fp32 row goes to every rank's receive area, every
+    // value tagged with the epoch (two values per 16-byte store; an aligned 8-byte word
+    // arrives whole, so a reader that sees the tag sees the value)
+    const size_t slot = sequence_exchange_slot_words(prm.gather_rows, D);
     const size_t off = ((size_t)(prm.gather_epoch & 1u) * prm.gather_world + prm.gather_rank) * slot +
                        (size_t)out_row * D + 4 * d4;
-    for (int p = 0; p < prm.gather_world; ++p)
-      *reinterpret_cast<float4*>(static_cast<float*>(prm.gather_out[p]) + off) = v;
+    const uint32_t e = prm.gather_epoch;
+    for (int p = 0; p < prm.gather_world; ++p) {
+      uint2* dst = static_cast<uint2*>(prm.gather_out[p]) + off;
+      st_volatile_v4(dst, __float_as_uint(v.x), e, __float_as_uint(v.y), e);
+      st_volatile_v4(dst + 2, __float_as_uint(v.z), e, __float_as_uint(v.w), e);
+    }
     return;
   }
   if (prm.gather_world > 0) {
@@ -349,10 +395,11 @@ __device__ __forceinline__ void store_final(const DecodeParams& prm, long long o
 template <int D>
 __device__ __forceinline__ void store_final_lse(const DecodeParams& prm, long long out_row, float lse) {
   if (prm.gather_world > 0 && prm.gather_mode == 1) {
-    const size_t slot = (size_t)prm.gather_rows * (D + 1);
+    const size_t slot = sequence_exchange_slot_words(prm.gather_rows, D);
     const size_t off = ((size_t)(prm.gather_epoch & 1u) * prm.gather_world + prm.gather_rank) * slot +
                        (size_t)prm.gather_rows * D + out_row;
-    for (int p = 0; p < prm.gather_world; ++p) static_cast<float*>(prm.gather_out[p])[off] = lse;
+    for (int p = 0; p < prm.gather_world; ++p)
+      st_volatile_v2(static_cast<uint2*>(prm.gather_out[p]) + off, __float_as_uint(lse), prm.gather_epoch);
     return;
   }
   if (prm.out_lse) prm.out_lse[out_row] = lse;
@@ -416,13 +463,69 @@ __device__ __forceinline__ void merge_small(const DecodeParams& prm, int first_s
   }
 }
 
-// Many partials (a single long sequence spreads every group over about twenty CTAs): the
-// same single round trip with kMergeWide partials per thread.  Kept out of line so that its
-// hundred-odd live registers do not weigh on the register allocation of the streaming loop;
-// the launch parameters are reached through their address in the parameter space.
+// More than kBatch partials, completion-ticket mode, inline: a first pass over the
+// log-sum-exps for the row's maximum, then the outputs kBatch at a time (one L2 round trip per
+// batch).  Used inside the streaming loop, where an out-of-line call would cost the loop
+// more than the merge gains.
+template <typename Q, int D, int kBatch>
+__device__ __forceinline__ void merge_rounds(const DecodeParams& prm, int first_slot, int n,
+                                             long long out_row0, int tid, int nthreads) {
+  const int G = prm.group;
+  constexpr int D4 = D / 4;
+  const float* lse_g = prm.part_lse + (size_t)first_slot * G;
+  for (int idx = tid; idx < G * D4; idx += nthreads) {
+    const int row = idx / D4, d4 = idx % D4;
+    const float4* o_g =
+        reinterpret_cast<const float4*>(prm.part_o + ((size_t)first_slot * G + row) * D) + d4;
+    float mx = -INFINITY;
+    for (int p = 0; p < n; ++p) mx = fmaxf(mx, ld_cg_f32(lse_g + (size_t)p * G + row));
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    for (int p0 = 0; p0 < n; p0 += kBatch) {
+      float4 o[kBatch];
+      float w[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int p = p0 + u;
+        if (p < n) {
+          o[u] = ld_cg_f32x4(o_g + (size_t)p * G * D4);
+          w[u] = fast_exp2((ld_cg_f32(lse_g + (size_t)p * G + row) - ms) * kLog2e);
+        } else {
+          o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          w[u] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        acc.x += w[u] * o[u].x;
+        acc.y += w[u] * o[u].y;
+        acc.z += w[u] * o[u].z;
+        acc.w += w[u] * o[u].w;
+        wsum += w[u];
+      }
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    store_final<Q, D>(prm, out_row0 + row, d4, acc);
+    if (d4 == 0)
+      store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+  }
+}
+
+// Many partials, completion-ticket mode (a single long sequence spreads every group over about
+// twenty CTAs): the same single round trip with kMergeWide partials per thread.  Kept out of
+// line so that its hundred-odd live registers do not weigh on the register allocation of the
+// streaming loop; the launch parameters are reached through their address in the parameter space.
 // More than kMergeWide partials: a first pass finds the row's largest log-sum-exp, then the
 // outputs come kMergeWide at a time.
-constexpr int kMergeWide = 24;
+#ifndef GQA_MERGE_WIDE
+#define GQA_MERGE_WIDE 24
+#endif
+constexpr int kMergeWide = GQA_MERGE_WIDE;
 template <typename Q, int D>
 __device__ __noinline__ void merge_group_wide(const DecodeParams* __restrict__ prmp, int first_slot,
                                               int n, long long out_row0, int tid, int nthreads) {
@@ -493,6 +596,227 @@ __device__ __noinline__ void merge_group_wide(const DecodeParams* __restrict__ p
     store_final<Q, D>(prm, out_row0 + row, d4, acc);
     if (d4 == 0)
       store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+  }
+}
+
+// A value stored into a polled partial: any bit pattern but zero (zero means "not here yet").
+__device__ __forceinline__ float not_zero(float v) {
+  return __float_as_uint(v) == 0u ? __uint_as_float(0x80000000u) : v;  // +0 -> -0
+}
+__device__ __forceinline__ float4 ld_volatile_f4(const float* p) {
+  const uint4 v = ld_volatile_v4(p);
+  return make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+}
+__device__ __forceinline__ float ld_volatile_f1(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Merge of a group whose partials announce themselves (DecodeParams::polled), run by one
+// designated contributor of the group once its own part is done.  All `nthreads` threads of
+// named barrier 1 call it together.  A thread fetches its four columns and the log-sum-exp of
+// up to kMergeWide partials at once and fetches again, until the time limit, whatever is
+// still zero; in the usual case everything is there at the first look and the merge costs
+// one L2 round trip, with no atomic and no fence on anybody's critical path.  The words are
+// handed back as zeros for the next launch.
+template <typename Q, int D, int kMergeWide>
+__device__ __forceinline__ void merge_polled_body(const DecodeParams& prm, int first_slot, int n,
+                                                  long long out_row0, int tid, int nthreads) {
+  const int G = prm.group;
+  constexpr int D4 = D / 4;
+  float* lse_g = prm.part_lse + (size_t)first_slot * G;
+  // Wait quietly: one thread per log-sum-exp word looks at it every few hundred nanoseconds
+  // (a CTA that polled all its words with all its threads would take L2 bandwidth from the
+  // CTAs it is waiting for).  Once the log-sum-exps are there the outputs are too, or nearly.
+  for (int i = tid; i < n * G; i += nthreads) {
+    const unsigned long long t0 = global_timer_ns();
+    unsigned pause = 64;
+    while (__float_as_uint(ld_volatile_f1(lse_g + i)) == 0u) {
+      if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // reported by the fetch below
+      __nanosleep(pause);
+      if (pause < 512) pause *= 2;
+    }
+  }
+  bar_sync(1, nthreads);
+  for (int idx = tid; idx < G * D4; idx += nthreads) {
+    const int row = idx / D4, d4 = idx % D4;
+    float* o_g = prm.part_o + ((size_t)first_slot * G + row) * D + 4 * d4;
+    const size_t o_step = (size_t)G * D;  // floats between consecutive partials
+    float mx = -INFINITY, wsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool complete = true;
+    for (int p0 = 0; p0 < n && complete; p0 += kMergeWide) {
+      float4 o[kMergeWide];
+      float l[kMergeWide];
+      unsigned pending = n - p0 >= kMergeWide ? (kMergeWide == 32 ? 0xffffffffu : (1u << kMergeWide) - 1u)
+                                              : (1u << (n - p0)) - 1u;
+      const unsigned long long t0 = global_timer_ns();
+      for (;;) {
+#pragma unroll
+        for (int u = 0; u < kMergeWide; ++u) {
+          if ((pending >> u) & 1u) {
+            l[u] = ld_volatile_f1(lse_g + (size_t)(p0 + u) * G + row);
+            o[u] = ld_volatile_f4(o_g + (size_t)(p0 + u) * o_step);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kMergeWide; ++u) {
+          if (((pending >> u) & 1u) && __float_as_uint(l[u]) != 0u && __float_as_uint(o[u].x) != 0u &&
+              __float_as_uint(o[u].y) != 0u && __float_as_uint(o[u].z) != 0u &&
+              __float_as_uint(o[u].w) != 0u)
+            pending &= ~(1u << u);
+        }
+        if (!pending) break;
+        if (global_timer_ns() - t0 > prm.wait_limit_ns) {
+          atomicOr(prm.status, kStatusWaitPartial);
+          complete = false;
+          break;
+        }
+        __nanosleep(100);
+      }
+      if (!complete) break;
+      // running maximum across batches of partials (one batch is the usual case)
+      float bm = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < kMergeWide; ++u)
+        if (p0 + u < n) bm = fmaxf(bm, l[u]);
+      const float mnew = fmaxf(mx, bm);
+      const float ms = (mnew == -INFINITY) ? 0.f : mnew;
+      if (p0 > 0) {
+        const float keep = fast_exp2((mx - ms) * kLog2e);
+        acc.x *= keep;
+        acc.y *= keep;
+        acc.z *= keep;
+        acc.w *= keep;
+        wsum *= keep;
+      }
+      mx = mnew;
+#pragma unroll
+      for (int u = 0; u < kMergeWide; ++u) {
+        if (p0 + u < n) {
+          const float w = fast_exp2((l[u] - ms) * kLog2e);
+          acc.x += w * o[u].x;
+          acc.y += w * o[u].y;
+          acc.z += w * o[u].z;
+          acc.w += w * o[u].w;
+          wsum += w;
+        }
+      }
+    }
+    if (!complete) continue;
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    store_final<Q, D>(prm, out_row0 + row, d4, acc);
+    if (d4 == 0)
+      store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+    for (int p = 0; p < n; ++p) {
+      *reinterpret_cast<float4*>(o_g + (size_t)p * o_step) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (d4 == 0) lse_g[(size_t)p * G + row] = 0.f;
+    }
+  }
+}
+// The merge as it runs after a CTA's streaming: out of line, so that its hundred-odd live
+// registers (kMergeWide partials per thread in flight) do not weigh on the register
+// allocation of the streaming loop; the launch parameters are reached through their address
+// in the parameter space.
+template <typename Q, int D>
+__device__ __noinline__ void merge_group_polled(const DecodeParams* __restrict__ prmp, int first_slot,
+                                                int n, long long out_row0, int tid, int nthreads) {
+  merge_polled_body<Q, D, kMergeWide>(*prmp, first_slot, n, out_row0, tid, nthreads);
+}
+
+// Sequence shards, end of the kernel: LSE-weighted merge of the `world` partials of this CTA's
+// share of the rows (the algebra of merge_rows_kernel, i.e. of gqa_decode/gqa_decode.py:661-669
+// one level up).  The partials sit in this rank's receive area as {value, epoch} words; a
+// thread fetches all sources of its (row, 4 columns) at once and fetches again, until a time
+// limit, whatever does not carry this step's epoch yet.  A row whose sources never all arrive
+// is left unwritten and the status word gets kStatusWaitExchange.
+template <typename Q, int D>
+__device__ __noinline__ void merge_sequence_shards(const DecodeParams* __restrict__ prmp, int tid,
+                                                   int nthreads) {
+  const DecodeParams& prm = *prmp;
+  constexpr int D4 = D / 4;
+  const int w = prm.gather_world;
+  const uint32_t e = prm.gather_epoch;
+  const long long rows = prm.gather_rows;
+  const size_t slot = sequence_exchange_slot_words(rows, D);
+  const uint2* part =
+      static_cast<const uint2*>(prm.gather_out[prm.gather_rank]) + (size_t)(e & 1u) * w * slot;
+  const long long r0 = rows * blockIdx.x / gridDim.x, r1 = rows * (blockIdx.x + 1) / gridDim.x;
+  for (long long idx = r0 * D4 + tid; idx < r1 * D4; idx += nthreads) {
+    const long long row = idx / D4;
+    const int d4 = (int)(idx % D4);
+    float4 o[kMaxPeers];
+    float l[kMaxPeers];
+    unsigned pending = (1u << w) - 1u;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+      uint2 lw[kMaxPeers];
+      uint4 a[kMaxPeers], b[kMaxPeers];
+#pragma unroll
+      for (int s = 0; s < kMaxPeers; ++s) {
+        if ((pending >> s) & 1u) {
+          const uint2* src = part + (size_t)s * slot;
+          lw[s] = ld_volatile_v2(src + (size_t)rows * D + row);
+          a[s] = ld_volatile_v4(src + (size_t)row * D + 4 * d4);
+          b[s] = ld_volatile_v4(src + (size_t)row * D + 4 * d4 + 2);
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < kMaxPeers; ++s) {
+        if (((pending >> s) & 1u) && lw[s].y == e && a[s].y == e && a[s].w == e && b[s].y == e &&
+            b[s].w == e) {
+          l[s] = __uint_as_float(lw[s].x);
+          o[s] = make_float4(__uint_as_float(a[s].x), __uint_as_float(a[s].z),
+                             __uint_as_float(b[s].x), __uint_as_float(b[s].z));
+          pending &= ~(1u << s);
+        }
+      }
+      if (!pending) break;
+      if (global_timer_ns() - t0 > prm.wait_limit_ns) {
+        atomicOr(prm.status, kStatusWaitExchange);
+        break;
+      }
+      __nanosleep(64);
+    }
+    if (pending) continue;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < kMaxPeers; ++s)
+      if (s < w) mx = fmaxf(mx, l[s]);
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxPeers; ++s) {
+      if (s < w) {
+        const float wt = fast_exp2((l[s] - ms) * kLog2e);
+        acc.x += wt * o[s].x;
+        acc.y += wt * o[s].y;
+        acc.z += wt * o[s].z;
+        acc.w += wt * o[s].w;
+        wsum += wt;
+      }
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    if (prm.out) {
+      uint2 pk;
+      pk.x = Mma16<Q>::pack(acc.x, acc.y);
+      pk.y = Mma16<Q>::pack(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<Q*>(prm.out) + row * D + 4 * d4) = pk;
+    }
+    if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + row * D + 4 * d4) = acc;
+    if (prm.out_lse && d4 == 0)
+      prm.out_lse[row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
   }
 }
 
@@ -782,6 +1106,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   TileDesc* sm_desc = reinterpret_cast<TileDesc*>(bars + 2 * kMaxStages);
   int* sm_flag = reinterpret_cast<int*>(sm_desc + kDescRing);
   volatile int* sm_published = sm_flag + 1;
+  volatile int* sm_deferred = sm_flag + 3;  // merges put off so far
+  int* sm_defer_list = sm_flag + 8;         // kDeferCap x {first slot, partials, first output row}
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
   const uint32_t stage_addr0 = smem_u32(stage0);
 
@@ -795,6 +1121,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       mbar_init(empty0 + 8 * s, kWarpsPerGroup);
     }
     *sm_published = 0;
+    *sm_deferred = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -862,12 +1189,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         d.n_parts = sg.n_parts;
         if (ntiles == 0) {
           d.valid = 0;
-          d.flags = kTileFirst | kTileLast;
+          d.flags = kTileFirst | kTileLast | (sg.first_slot < u0 ? kTileShared : 0);
           pr.post(d, 0);
         }
         for (int t = 0; t < ntiles; ++t) {
           d.valid = min(TILE, rows - t * TILE);
-          d.flags = (t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0);
+          d.flags = (t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0) |
+                    (sg.first_slot < u0 ? kTileShared : 0);
           if (paged) pr.post_paged(d, sg.row_begin + t * TILE);
           else pr.post(d, sg.kv_row0 + sg.row_begin + (long long)t * TILE);
         }
@@ -900,25 +1228,41 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             continue;
           }
           const int gi = wk.b * Hkv + wk.h;
+          const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           if (gi != cached_group) {
-            // per-group values (a few 64-bit divisions) are computed once per group
+            // per-group values are computed once per group
             cached_group = gi;
             d.b = wk.b;
             d.h = wk.h;
             d.ntg = wk.ntg;
-            d.first_slot = wk.group_first_slot();
+            row0 = wk.kv_row0();
+            // The slot fields take four divisions - a microsecond or two of dependent integer
+            // code on one thread - and the consumers read them at the end of a segment only:
+            // unless this tile already ends the segment, it is sent on its way first.
+            const bool early = !last;
+            if (early) {
+              d.valid = min(TILE, wk.len - wk.ti * TILE);
+              d.flags = (open ? 0 : kTileFirst) | kTileShared;
+              if (paged) pr.post_paged(d, wk.ti * TILE);
+              else pr.post(d, row0 + (long long)wk.ti * TILE);
+            }
             if (prm.sched.steal) {
+              d.first_slot = wk.group_first_slot();
               d.slot = -1;
               d.n_parts = 0;
             } else {
-              d.slot = d.first_slot + wk.group_static_index(cta);
-              d.n_parts = wk.group_static_parts();
+              int index;
+              wk.group_static_slots(cta, d.first_slot, d.n_parts, index);
+              d.slot = d.first_slot + index;
             }
-            row0 = wk.kv_row0();
+            if (early) {
+              open = true;
+              wk.advance();
+              continue;
+            }
           }
-          const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           d.valid = min(TILE, wk.len - wk.ti * TILE);
-          d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0);
+          d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0) | kTileShared;
           if (paged) pr.post_paged(d, wk.ti * TILE);
           else pr.post(d, row0 + (long long)wk.ti * TILE);
           open = !last;
@@ -954,6 +1298,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int r0 = lane >> 2, c = lane & 3;
   const int Hq = prm.num_q_heads;
   const bool dynamic = prm.sched.num_splits == 0 && prm.sched.steal;
+  const bool polled = prm.polled != 0;
 
   // Sequences without keys own no tiles in the balanced schedule: their outputs are zeros.
   if (prm.sched.num_splits == 0 && prm.sched.seq_lens) {
@@ -980,7 +1325,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #endif
 
   uint32_t s = 0, ph = 0;  // stage of tile `it` and the parity of its use
-  for (uint32_t it = 0;; ++it, next_stage(s, ph, nst)) {
+  uint32_t it = 0;  // descriptors consumed so far
+  for (;; ++it, next_stage(s, ph, nst)) {
     // The descriptor is published before the tile's loads are even issued, so it is read
     // first: a new segment's query rows are then fetched while the tile is still in flight.
     bool ok = true;
@@ -1116,9 +1462,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         acc.z += v.z;
         acc.w += v.w;
       }
-      if (direct) store_final<Q, D>(prm, out_row0 + row, d4, acc);
-      else if (slot >= 0)
+      if (direct) {
+        store_final<Q, D>(prm, out_row0 + row, d4, acc);
+      } else if (slot >= 0) {
+        if (polled) acc = make_float4(not_zero(acc.x), not_zero(acc.y), not_zero(acc.z), not_zero(acc.w));
         *reinterpret_cast<float4*>(prm.part_o + ((size_t)slot * G + row) * D + 4 * d4) = acc;
+      }
     }
     if (tid < G) {
       float M = -INFINITY;
@@ -1133,7 +1482,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (direct) {
         store_final_lse<D>(prm, out_row0 + tid, lse);
       } else if (slot >= 0) {
-        prm.part_lse[(size_t)slot * G + tid] = lse;
+        prm.part_lse[(size_t)slot * G + tid] = polled ? not_zero(lse) : lse;
       }
     }
     if (!prm.fused_merge && tid == 0) {
@@ -1141,35 +1490,79 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       else if (slot == d.first_slot) prm.group_info[g] = make_int2(d.first_slot, d.n_parts);
     }
     if (!direct && prm.fused_merge) {
-      // publish the partial, then draw a ticket: tiles covered (stealing schedule) or one
-      // per partial (static schedules); whoever completes the group merges it.  The CTA
-      // barrier orders all threads' partial stores before thread 0's release-acquire
-      // ticket, and the barrier after it hands the acquired view to the other threads.
-      bar_sync(1, kConsumerThreads);
-      if (tid == 0) {
-        const int add = dynamic ? seg_tiles : 1, want = dynamic ? d.ntg : d.n_parts;
-        const int before = atom_add_acq_rel(prm.tickets + g, add);
-        int n = 0;
-        if (before + add == want) {
-          n = dynamic ? atomicAdd(prm.alloc + g, 0) : d.n_parts;
-          if (n < 0 || d.first_slot + n > prm.num_slots) {
-            atomicOr(prm.status, kStatusSlotRange);
-            n = 0;
+      if (polled) {
+        // The partial announces itself; one contributor merges the group.  Balanced schedule:
+        // the CTA that wrote the group's FIRST partial - its share of the group is the end
+        // of its range, so by then the partial of the CTA holding the group's tail (the start
+        // of that CTA's range) is long there and the ones in between arrive at the same
+        // moment; it merges after its last tile.  Explicit splits: the CTA holding the LAST
+        // piece - the earlier pieces are its own, already written (merge on the spot), or a
+        // lower CTA's (merge after the last tile).
+        const bool mine = prm.sched.num_splits > 0 ? slot == d.first_slot + d.n_parts - 1
+                                                   : slot == d.first_slot;
+        if (mine && (d.flags & kTileShared)) {
+          if (tid == 0) {
+            const int at = *sm_deferred;  // never more than one per CTA
+            if (at < kDeferCap) {
+              sm_defer_list[3 * at] = d.first_slot;
+              sm_defer_list[3 * at + 1] = d.n_parts;
+              sm_defer_list[3 * at + 2] = (int)out_row0;
+              *sm_deferred = at + 1;
+            } else {
+              atomicOr(prm.status, kStatusSlotRange);
+            }
           }
-          prm.tickets[g] = 0;  // every contributor has arrived: leave the counters clean
-          prm.alloc[g] = 0;
+        } else if (mine) {
+          merge_polled_body<Q, D, 4>(prm, d.first_slot, d.n_parts, out_row0, tid, kConsumerThreads);
         }
-        *sm_flag = n;
+      } else {
+        // completion tickets: publish the partial, then count tiles covered (stealing
+        // schedule) or partials (static schedules); whoever completes the group merges it.
+        // The CTA barrier orders all threads' partial stores before thread 0's
+        // release-acquire ticket, and the barrier after it hands the acquired view to the
+        // other threads.
+        bar_sync(1, kConsumerThreads);
+        if (tid == 0) {
+          const int add = dynamic ? seg_tiles : 1, want = dynamic ? d.ntg : d.n_parts;
+          const int before = atom_add_acq_rel(prm.tickets + g, add);
+          int n = 0;
+          if (before + add == want) {
+            n = dynamic ? atomicAdd(prm.alloc + g, 0) : d.n_parts;
+            if (n < 0 || d.first_slot + n > prm.num_slots) {
+              atomicOr(prm.status, kStatusSlotRange);
+              n = 0;
+            }
+            prm.tickets[g] = 0;  // every contributor has arrived: leave the counters clean
+            prm.alloc[g] = 0;
+            if (n > 0 && prm.timestamps) prm.timestamps[kTimestampWords * blockIdx.x + 5] = global_timer_ns();
+          }
+          *sm_flag = n;
+        }
+        bar_sync(1, kConsumerThreads);
+        const int n = *sm_flag;
+        if (n > Tr::kMergeBatch)
+          merge_rounds<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
+        else if (n > 0)
+          merge_small<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
       }
-      bar_sync(1, kConsumerThreads);
-      const int n = *sm_flag;
-      if (n > Tr::kMergeBatch)
-        merge_group_wide<Q, D>(&prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
-      else if (n > 0)
-        merge_small<Q, D, Tr::kMergeBatch>(prm, d.first_slot, n, out_row0, tid, kConsumerThreads);
     }
     // sm_ml / sm_o / sm_flag are rewritten only after the next segment's barriers.
     bar_sync(1, kConsumerThreads);
+  }
+
+  // ---- the group merges that were put off (every consumer thread sees the same list: it was
+  // last changed before the barrier that ended the last segment)
+  {
+    const int todo = *sm_deferred;
+    if (todo > 0 && prm.timestamps && tid == 0)
+      prm.timestamps[kTimestampWords * blockIdx.x + 5] = global_timer_ns();
+    for (int e = 0; e < todo; ++e) {
+      const int first_slot = sm_defer_list[3 * e], n = sm_defer_list[3 * e + 1];
+      const long long row0 = sm_defer_list[3 * e + 2];
+      // (out of line except in the E4M3 kernels, whose consumers have no registers to spare)
+      if (Tr::kFp8) merge_polled_body<Q, D, 8>(prm, first_slot, n, row0, tid, kConsumerThreads);
+      else merge_group_polled<Q, D>(&prm, first_slot, n, row0, tid, kConsumerThreads);
+    }
   }
 
 #ifdef GQA_PROFILE_WAITS
@@ -1179,7 +1572,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     ts[4] = (unsigned long long)(clock64() - cc0);
   }
 #endif
-  if (prm.gather_world > 0) {
+  if (prm.gather_world > 0 && prm.gather_mode == 1) {
+    // sequence shards: every final row of this launch has been pushed to all ranks already
+    merge_sequence_shards<Q, D>(&prm, tid, kConsumerThreads);
+  } else if (prm.gather_world > 0) {
     // Hand-off of the gathered outputs: every thread's peer stores are fenced at system scope;
     // in the last CTA to get here, thread p raises this rank's flag on peer p (one fence, then
     // a plain system-scope store: eight release stores in a row would pay eight fences) and
@@ -1192,7 +1588,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int last = before == (int)gridDim.x - 1;
       if (last) *prm.done_ctas = 0;
       *sm_flag = last;
-      sm_flag[2] = 1;
     }
     bar_sync(1, kConsumerThreads);
     const int w = prm.gather_world;
@@ -1200,73 +1595,26 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (*sm_flag && tid < w) {
       __threadfence_system();
       st_relaxed_sys(prm.gather_flags[tid] + par * w + prm.gather_rank, prm.gather_epoch);
-    }
-    // head gather: only the last CTA has to see the peers' flags before the kernel may end;
-    // sequence shards: every CTA needs all partials before it merges its rows
-    int arrived = 1;
-    if ((*sm_flag || prm.gather_mode == 1) && tid < w) {
+      // only the last CTA has to see the peers' flags before the kernel may end
       const unsigned* mine = prm.gather_flags[prm.gather_rank] + par * w + tid;
       const unsigned long long t0 = global_timer_ns();
       while (ld_acquire_sys(mine) != prm.gather_epoch) {
         if (global_timer_ns() - t0 > prm.wait_limit_ns) {
           atomicOr(prm.status, kStatusWaitExchange);
-          arrived = 0;
           break;
         }
         __nanosleep(100);
       }
     }
-    if (prm.gather_mode == 1) {
-      // LSE-weighted merge of the `world` partials of this CTA's share of the rows (the
-      // algebra of merge_rows_kernel, i.e. of gqa_decode/gqa_decode.py:661-669 one level up)
-      // all partials have landed only if no waiting thread gave up (sm_flag[2]: third word of
-      // the flag area, set to 1 above)
-      if (!arrived) sm_flag[2] = 0;
-      bar_sync(1, kConsumerThreads);
-      if (sm_flag[2]) {
-        constexpr int D4 = D / 4;
-        const long long rows = prm.gather_rows;
-        const size_t slot = (size_t)rows * (D + 1);
-        const float* part = static_cast<const float*>(prm.gather_out[prm.gather_rank]) + (size_t)par * w * slot;
-        const long long r0m = rows * blockIdx.x / gridDim.x, r1m = rows * (blockIdx.x + 1) / gridDim.x;
-        for (long long idx = r0m * D4 + tid; idx < r1m * D4; idx += kConsumerThreads) {
-          const long long row = idx / D4;
-          const int d4 = (int)(idx % D4);
-          float mx = -INFINITY;
-          for (int sidx = 0; sidx < w; ++sidx) mx = fmaxf(mx, __ldcg(part + sidx * slot + (size_t)rows * D + row));
-          const float ms = (mx == -INFINITY) ? 0.f : mx;
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          float wsum = 0.f;
-          for (int sidx = 0; sidx < w; ++sidx) {
-            const float l = __ldcg(part + sidx * slot + (size_t)rows * D + row);
-            const float4 o = __ldcg(reinterpret_cast<const float4*>(part + sidx * slot + row * D) + d4);
-            const float wt = fast_exp2((l - ms) * kLog2e);
-            acc.x += wt * o.x;
-            acc.y += wt * o.y;
-            acc.z += wt * o.z;
-            acc.w += wt * o.w;
-            wsum += wt;
-          }
-          const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-          acc.x *= inv;
-          acc.y *= inv;
-          acc.z *= inv;
-          acc.w *= inv;
-          if (prm.out) {
-            uint2 pk;
-            pk.x = Mma16<Q>::pack(acc.x, acc.y);
-            pk.y = Mma16<Q>::pack(acc.z, acc.w);
-            *reinterpret_cast<uint2*>(reinterpret_cast<Q*>(prm.out) + row * D + 4 * d4) = pk;
-          }
-          if (prm.out_f32) *reinterpret_cast<float4*>(prm.out_f32 + row * D + 4 * d4) = acc;
-          if (prm.out_lse && d4 == 0)
-            prm.out_lse[row] = wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY;
-        }
-      }
-    }
   }
   if (tid == 0) {
-    if (prm.timestamps) prm.timestamps[kTimestampWords * blockIdx.x + 4] = global_timer_ns();
+    if (prm.timestamps) {
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      prm.timestamps[kTimestampWords * blockIdx.x + 4] = global_timer_ns();
+      prm.timestamps[kTimestampWords * blockIdx.x + 6] = smid;
+      prm.timestamps[kTimestampWords * blockIdx.x + 7] = it;
+    }
     // work stealing only: the last CTA to finish leaves the chunk deques clean for the
     // next launch
     if (dynamic) {

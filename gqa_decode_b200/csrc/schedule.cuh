@@ -41,6 +41,21 @@
 
 namespace gqa {
 
+// Quotient (and remainder) of non-negative line positions.  A 64-bit division is a long
+// software routine on the GPU (the better part of a microsecond of dependent instructions,
+// and a CTA's set-up performs a dozen before its first load can be issued); nearly every
+// operand here fits 32 bits, where the division is a short inline sequence.
+GQA_HD long long idiv(long long a, long long b) {
+  if ((((unsigned long long)a | (unsigned long long)b) >> 32) == 0)
+    return (long long)((unsigned)a / (unsigned)b);
+  return a / b;
+}
+GQA_HD long long imod(long long a, long long b) {
+  if ((((unsigned long long)a | (unsigned long long)b) >> 32) == 0)
+    return (long long)((unsigned)a % (unsigned)b);
+  return a % b;
+}
+
 enum KvLayout : int {
   kLayoutPadded = 0,  // K/V [batch, Hkv, max_seq, D]: head slab of (b,h) starts at row (b*Hkv+h)*max_seq
   kLayoutPacked = 1,  // K/V [sum_b Hkv*len_b, D]: sequence b holds [Hkv, len_b, D] after all earlier sequences
@@ -126,25 +141,25 @@ struct Walker {
       return;
     }
     const long long c = p.chunk_tiles > 0 ? p.chunk_tiles : 1;
-    n_chunks = (total + c - 1) / c;
+    n_chunks = idiv(total + c - 1, c);
     parts = n_chunks < p.num_ctas ? n_chunks : p.num_ctas;
   }
   GQA_HD long long chunk_tiles() const { return p.chunk_tiles > 0 ? p.chunk_tiles : 1; }
   // chunk (balanced) or unit (explicit) range owned by CTA c
   GQA_HD void cta_range(int c, long long& q0, long long& q1) const {
     if (p.num_splits > 0) {
-      q0 = (c * total) / p.num_ctas;
-      q1 = ((c + 1) * total) / p.num_ctas;
+      q0 = idiv(c * total, p.num_ctas);
+      q1 = idiv((c + 1) * total, p.num_ctas);
     } else if (c < parts) {
-      q0 = (c * n_chunks) / parts;
-      q1 = ((c + 1) * n_chunks) / parts;
+      q0 = idiv(c * n_chunks, parts);
+      q1 = idiv((c + 1) * n_chunks, parts);
     } else {
       q0 = q1 = 0;
     }
   }
   // owner of chunk q: largest c with floor(c*M/P) <= q (P <= M: every owner has chunks)
   GQA_HD long long cta_of_chunk(long long q) const {
-    return ((q + 1) * parts - 1) / n_chunks;
+    return idiv((q + 1) * parts - 1, n_chunks);
   }
   GQA_HD void chunk_tile_range(long long q, long long& t0, long long& t1) const {
     t0 = q * chunk_tiles();
@@ -162,15 +177,26 @@ struct Walker {
   // no partial)
   GQA_HD long long group_first_tile_unit() const { return tiles_before_group + overhead(); }
   GQA_HD int group_first_slot() const {
-    return (int)(group_first_tile_unit() / chunk_tiles() + group_index());
+    return (int)(idiv(group_first_tile_unit(), chunk_tiles()) + group_index());
   }
   GQA_HD int group_static_parts() const {
     const long long c = chunk_tiles();
-    return (int)(cta_of_chunk((group_first_tile_unit() + ntg - 1) / c) -
-                 cta_of_chunk(group_first_tile_unit() / c) + 1);
+    return (int)(cta_of_chunk(idiv(group_first_tile_unit() + ntg - 1, c)) -
+                 cta_of_chunk(idiv(group_first_tile_unit(), c)) + 1);
   }
   GQA_HD int group_static_index(int cta) const {
-    return (int)(cta - cta_of_chunk(group_first_tile_unit() / chunk_tiles()));
+    return (int)(cta - cta_of_chunk(idiv(group_first_tile_unit(), chunk_tiles())));
+  }
+  // The three values above in one go (four divisions instead of seven): first slot of the
+  // current group, how many partials the static schedule makes of it, and which of them CTA
+  // `cta` writes.
+  GQA_HD void group_static_slots(int cta, int& first_slot, int& n_parts, int& index) const {
+    const long long c = chunk_tiles(), u0 = group_first_tile_unit();
+    const long long q_first = idiv(u0, c), q_last = idiv(u0 + ntg - 1, c);
+    const long long c_first = cta_of_chunk(q_first), c_last = cta_of_chunk(q_last);
+    first_slot = (int)(q_first + group_index());
+    n_parts = (int)(c_last - c_first + 1);
+    index = (int)(cta - c_first);
   }
 
   // ---- positioning on unit t0 of the line (balanced) ---------------------------------
@@ -185,8 +211,8 @@ struct Walker {
     ntg = tiles_of(len);
     const int ung = ntg + overhead();
     const long long off = t0 - s_tiles_before;
-    h = (int)(off / ung);
-    ui = (int)(off % ung);
+    h = (int)idiv(off, ung);
+    ui = (int)(off - (long long)h * ung);
     ti = ui - overhead();
     tiles_before_group = s_tiles_before + (long long)h * ung;
   }
@@ -242,7 +268,7 @@ struct Walker {
   // explicit mode: position on unit u (units are visited in increasing order)
   GQA_HD void seek_unit_serial(long long u) {
     unit = u;
-    const int nb = (int)(u / p.num_splits / p.num_kv_heads);
+    const int nb = (int)idiv(idiv(u, p.num_splits), p.num_kv_heads);
     for (; sb < nb && sb < p.batch; ++sb) s_rows_before += len_of(sb);
     b = sb;
     rows_before_seq = s_rows_before;
@@ -298,7 +324,7 @@ struct Walker {
   __device__ __forceinline__ void seek_unit_warp(long long u) {
     const int lane = threadIdx.x & 31;
     unit = u;
-    const int nb = (int)(u / p.num_splits / p.num_kv_heads);
+    const int nb = (int)idiv(idiv(u, p.num_splits), p.num_kv_heads);
     long long r = 0;
     for (int bb = sb + lane; bb < nb && bb < p.batch; bb += 32) r += len_of(bb);
     for (int o = 16; o; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
@@ -312,14 +338,14 @@ struct Walker {
   // explicit mode: describe unit `unit` and move to the next one
   GQA_HD void next_unit(Segment& s) {
     const int T = p.tile_rows, K = p.num_splits;
-    const long long g = unit / K;
-    const int sp = (int)(unit % K);
-    const int nb = (int)(g / p.num_kv_heads);
+    const long long g = idiv(unit, K);
+    const int sp = (int)(unit - g * K);
+    const int nb = (int)idiv(g, p.num_kv_heads);
     while (b < nb) {
       rows_before_seq += len_of(b);
       ++b;
     }
-    h = (int)(g % p.num_kv_heads);
+    h = (int)(g - (long long)nb * p.num_kv_heads);
     len = len_of(b);
     ntg = tiles_of(len);
     const int cs = (ntg + K - 1) / K;

@@ -228,8 +228,9 @@ class FusedSequenceExchange:
     """Sequence-sharded decode in ONE kernel per rank and step
     (``gqa_decode_attention_gather`` with ``GQA_GATHER_SEQUENCE``): while a rank streams its
     slice of the keys, every finished row (normalised fp32 output + log-sum-exp) is pushed into
-    all ranks' receive areas with plain peer stores; the kernel's tail raises the flags, waits
-    (bounded) for the peers' and merges the ``world`` partials into the final output.  Replaces
+    all ranks' receive areas with plain peer stores, each value tagged with the step's epoch so
+    that the data is its own arrival flag; the kernel's tail merges the ``world`` partials into
+    the final output, waiting (bounded) for values that have not landed yet.  Replaces
     decode kernel + :class:`NvlinkExchange` kernel (or two NCCL all-gathers + merge).
 
     Collective constructor (same ``batch``, ``num_q_heads``, ``head_dim`` on every rank); one
@@ -253,8 +254,9 @@ class FusedSequenceExchange:
         self.device = torch.device(device)
         self.shape = (int(batch), int(num_q_heads), int(head_dim))
         rows = self.shape[0] * self.shape[1]
-        self.recv = symm_mem.empty(2 * self.world * rows * (self.shape[2] + 1), dtype=torch.float32,
-                                   device=self.device)
+        nbytes = int(_native.load().gqa_sequence_exchange_bytes(self.world, rows, self.shape[2]))
+        self.recv = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=self.device)
+        self.recv.zero_()  # every word's epoch tag starts at 0; epochs start at 1
         self.flags = symm_mem.empty(2 * self.world, dtype=torch.int32, device=self.device)
         self.flags.zero_()
         self._recv_handle = symm_mem.rendezvous(self.recv, self.group)

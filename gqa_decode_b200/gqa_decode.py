@@ -111,28 +111,25 @@ def reduce_partials(partial_out, partial_max, partial_sum, num_q_heads, num_spli
 _DTYPE_CODE = {torch.bfloat16: _native.DTYPE_BF16, torch.float16: _native.DTYPE_FP16}
 
 # The C library keeps no record of workspaces; this layer owns them and knows what they last
-# held.  A workspace's control words must be zero at launch, kernels leave them zero, and
-# their extent depends on the launch geometry: the "geometry key" below is that extent plus
-# the workspace size.  A launch whose key differs from the workspace's previous one, or whose
-# workspace has unknown contents, carries GQA_FLAG_CLEAR_WORKSPACE.
+# held.  What a launch uses of its workspace must be zero at launch and kernels leave it
+# zero, but where control words and partials lie depends on the launch geometry (sizes, CTA
+# count, split count, merge mode): the "geometry key" below.  A launch whose key differs from
+# the workspace's previous one, or whose workspace has unknown contents, carries
+# GQA_FLAG_CLEAR_WORKSPACE.
 _workspaces: dict = {}                       # (device type, index) -> [tensor, geometry key]
-_caller_workspaces = weakref.WeakKeyDictionary()  # caller-owned tensor -> geometry key
+_caller_workspaces: dict = {}  # id(caller-owned tensor) -> (weak reference to it, geometry key)
 
 
 @functools.lru_cache(maxsize=256)
-def _workspace_sizes(batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, device_index):
-    """(bytes needed, extent of the control words) for a launch geometry on a device."""
-    lib = _native.load()
-    need, ctrl = ctypes.c_size_t(0), ctypes.c_size_t(0)
+def _workspace_need(batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, device_index):
+    """Bytes of workspace a launch geometry needs on a device (cached: the drop-in entry
+    would otherwise ask the library on every call)."""
+    need = ctypes.c_size_t(0)
     _native.check(
-        lib.gqa_decode_workspace_bytes(
+        _native.load().gqa_decode_workspace_bytes(
             batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, ctypes.byref(need)),
         "gqa_decode_workspace_bytes")
-    _native.check(
-        lib.gqa_decode_workspace_control_bytes(
-            batch, num_q_heads, num_kv_heads, head_dim, num_splits, num_ctas, ctypes.byref(ctrl)),
-        "gqa_decode_workspace_control_bytes")
-    return need.value, ctrl.value
+    return need.value
 
 
 def workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_splits=0, num_ctas=0) -> int:
@@ -168,8 +165,14 @@ def _needs_clear(ws: torch.Tensor, device: torch.device, geometry) -> bool:
         clear = entry[1] is not None and entry[1] != geometry  # None: still all zeros
         entry[1] = geometry
         return clear
-    clear = _caller_workspaces.get(ws) != geometry
-    _caller_workspaces[ws] = geometry
+    # (keyed by identity: tensors compare element-wise, so they cannot key a weak dictionary)
+    known = _caller_workspaces.get(id(ws))
+    clear = known is None or known[0]() is not ws or known[1] != geometry
+    if known is None or known[0]() is not ws:
+        key = id(ws)
+        _caller_workspaces[key] = (weakref.ref(ws, lambda _, key=key: _caller_workspaces.pop(key, None)), geometry)
+    else:
+        _caller_workspaces[id(ws)] = (known[0], geometry)
     return clear
 
 
@@ -183,7 +186,7 @@ def reset_workspace(workspace: Optional[torch.Tensor] = None, device=None) -> No
             return
         workspace, entry[1] = entry[0], None
     else:
-        _caller_workspaces.pop(workspace, None)
+        _caller_workspaces.pop(id(workspace), None)
     with torch.cuda.device(workspace.device):
         _native.check(
             _native.load().gqa_decode_workspace_reset(
@@ -242,6 +245,7 @@ def gqa_decode_attention_batched(
     work_stealing: bool = False,
     block_table: Optional[torch.Tensor] = None,
     dependent_launch: bool = False,
+    ticket_merge: bool = False,
     wait_limit_ns: int = 0,
     _timestamps: Optional[torch.Tensor] = None,
     _entry: str = "auto",
@@ -277,6 +281,9 @@ def gqa_decode_attention_batched(
     dependent_launch: launch with programmatic stream serialization, so that the kernel's
       prologue overlaps the end of the previous kernel on the stream (it waits for that kernel
       before reading inputs); for back-to-back decode steps.
+    ticket_merge: detect complete groups with atomic tickets instead of letting the partials
+      announce themselves (the default, which keeps atomics and fences off the critical path
+      but needs the workspace's partial area to be zero at launch; this module sees to that).
     wait_limit_ns: bound on every wait inside the kernel (0 = two seconds); on expiry the
       status word (:func:`read_status`) is non-zero and the outputs are invalid.
     workspace: a caller-owned uint8 CUDA tensor of :func:`workspace_bytes` bytes instead of
@@ -371,8 +378,8 @@ def gqa_decode_attention_batched(
         raise ValueError("num_splits must be positive")
 
     dev = q.device
-    need, ctrl = _workspace_sizes(batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas,
-                                  _device_key(dev)[1])
+    need = _workspace_need(batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas,
+                           _device_key(dev)[1])
     if workspace is not None:
         ws = workspace
     elif _plan_only:
@@ -384,7 +391,9 @@ def gqa_decode_attention_batched(
     ws_bytes = ws.numel() * ws.element_size()
     if ws_bytes < need:
         raise ValueError(f"workspace too small: need {need} bytes")
-    clear = (workspace is not None or not _plan_only) and _needs_clear(ws, dev, (ctrl, ws_bytes))
+    mode = (bool(separate_merge), bool(_no_merge), bool(work_stealing), bool(ticket_merge))
+    geometry = (batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas, mode, ws_bytes)
+    clear = (workspace is not None or not _plan_only) and _needs_clear(ws, dev, geometry)
     if _gather is not None and _gather.mode == _native.GATHER_HEADS:
         out = None  # final rows go to the gathered buffers of every rank (distributed.HeadGather)
     elif out is None:
@@ -411,6 +420,7 @@ def gqa_decode_attention_batched(
         _native.FLAG_FP8_EXACT_V if fp8_exact_v else 0) | (
         _native.FLAG_WORK_STEALING if work_stealing else 0) | (
         _native.FLAG_CLEAR_WORKSPACE if clear else 0) | (
+        _native.FLAG_TICKET_MERGE if ticket_merge else 0) | (
         _native.FLAG_DEPENDENT_LAUNCH if dependent_launch else 0)
     a.wait_limit_ns = int(wait_limit_ns)
     a.debug_timestamps = _timestamps.data_ptr() if _timestamps is not None else None

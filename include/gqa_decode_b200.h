@@ -53,6 +53,13 @@ extern "C" {
                                      stream, after the arguments have been checked) before the
                                      launch: for a workspace whose contents are unknown, or that
                                      last served a launch of another geometry */
+#define GQA_FLAG_TICKET_MERGE 64   /* find out that a group's partials are complete with atomic
+                                     tickets.  Default for the static schedules is cheaper: partials
+                                     announce themselves (a word that is not zero has arrived) and
+                                     the CTA that writes a group's last partial polls for the rest,
+                                     which needs the workspace's partial area to be all zero at
+                                     launch (kernels leave it so); with tickets only the control
+                                     words need to be zero */
 #define GQA_FLAG_DEPENDENT_LAUNCH 32 /* launch with programmatic stream serialization: the kernel's
                                      prologue (and, for uniform lengths, its scheduling) overlaps the
                                      end of the previous kernel on the stream; it waits for that
@@ -105,35 +112,34 @@ typedef struct gqa_decode_args {
   uint64_t wait_limit_ns;      /* bound on every wait inside the kernel (a tile that never lands,
                                   a peer GPU's flag); on expiry a status bit is set and the
                                   kernel returns.  0: two seconds */
-  uint64_t* debug_timestamps;  /* optional diagnostics: device buffer of 6 * num_ctas uint64; per
+  uint64_t* debug_timestamps;  /* optional diagnostics: device buffer of 8 * num_ctas uint64; per
                                   CTA {prologue done, first load issued, first tile landed, start
-                                  of the last segment's epilogue, end, unused} in %globaltimer ns */
+                                  of the last segment's epilogue, end, ticket drawn before the
+                                  CTA's last merge or 0} in %globaltimer ns, then {SM id, tiles
+                                  consumed} */
 } gqa_decode_args_t;
 
 /*
  * Bytes of device scratch a launch with these sizes needs (partials, tickets, status).
  *
- * Workspace contract.  The library keeps no record of workspaces.  The front of a
- * workspace holds control words (status, tickets, counters) that must be ZERO when a launch
- * starts; kernels leave them zero when they finish with status 0.  How far the control
- * words reach depends on the launch geometry (gqa_decode_workspace_control_bytes), and
- * partial results of one geometry may lie where another geometry keeps control words.  So:
- * zero a workspace when it is created (gqa_decode_workspace_reset), and set
- * GQA_FLAG_CLEAR_WORKSPACE (or call gqa_decode_workspace_reset) on the first launch after
- * the geometry - batch, head counts, head_dim, num_splits, num_ctas, workspace_bytes -
- * changed and after a launch that reported a non-zero status.  A workspace serves one
- * launch at a time: launches that may overlap on the GPU need one each.
+ * Workspace contract.  The library keeps no record of workspaces.  A workspace holds
+ * control words (status, tickets, counters) and partial results; what a launch uses of it
+ * must be ZERO when the launch starts, and kernels leave it zero when they finish with
+ * status 0 (the default in-kernel merge hands its partials back as zeros; launches with
+ * GQA_FLAG_SEPARATE_MERGE, _NO_MERGE, _WORK_STEALING or _TICKET_MERGE need only the control
+ * words zero and leave their partials behind).  Where control words and partials lie depends
+ * on the launch geometry.  So: zero a workspace when it is created
+ * (gqa_decode_workspace_reset), and set GQA_FLAG_CLEAR_WORKSPACE (or call
+ * gqa_decode_workspace_reset) on the first launch after the geometry - batch, head counts,
+ * head_dim, num_splits, num_ctas, workspace_bytes, the merge flags - changed and after a
+ * launch that reported a non-zero status.  GQA_FLAG_CLEAR_WORKSPACE zeroes exactly what the
+ * launch uses (tens of megabytes for the default merge, a few kilobytes otherwise).  A
+ * workspace serves one launch at a time: launches that may overlap on the GPU need one each.
  */
 int gqa_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                int32_t head_dim, int32_t num_splits, int32_t num_ctas,
                                size_t* bytes);
 
-/* Extent of the control words (bytes from the start of the workspace) for these sizes: what
- * GQA_FLAG_CLEAR_WORKSPACE zeroes.  Two launches with equal extents on a workspace of equal
- * size may follow each other without clearing. */
-int gqa_decode_workspace_control_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
-                                       int32_t head_dim, int32_t num_splits, int32_t num_ctas,
-                                       size_t* bytes);
 
 /*
  * Byte offsets inside a workspace for explicit splits (num_splits = K > 0): offsets[0]
@@ -154,7 +160,8 @@ int gqa_decode_workspace_reset(void* workspace, size_t workspace_bytes, void* st
 /* Copy the status word back (synchronises the stream): 0 = ok, else OR of
  * 1 (consumer wait expired), 2 (producer wait expired), 4 (shared-memory misalignment),
  * 8 (a partial-slot index was out of range: the control words were not clean),
- * 16 (a peer GPU's flag never arrived: sequence exchange, head gather). */
+ * 16 (a peer GPU's flag never arrived: sequence exchange, head gather),
+ * 32 (a partial never arrived at the CTA merging its group: the workspace was not clean). */
 int gqa_decode_read_status(const void* workspace, void* stream, int32_t* status);
 
 /* bf16 / fp16 K and V.  Replaces gqa_decode_attention, gqa_decode/gqa_decode.py:672-762
@@ -251,13 +258,15 @@ int gqa_quantize_kv_fp8(const void* x, int32_t x_dtype, int64_t num_heads, int64
 #define GQA_GATHER_HEADS 0    /* ranks own KV heads; outputs are gathered (described above) */
 #define GQA_GATHER_SEQUENCE 1 /* ranks own contiguous key ranges of every head: rank r's
                                  normalised fp32 rows and log-sum-exps are pushed into every
-                                 rank's receive area peer_out[p] (floats, [2 parities][world]
-                                 [batch * num_q_heads * (head_dim + 1)]: outputs, then LSEs) as
-                                 they are produced; after the flags every CTA merges its share of
-                                 the rows (LSE-weighted, the reference's reduce_partials algebra,
-                                 gqa_decode/gqa_decode.py:661-669, across ranks) into args->out /
-                                 out_f32 / out_lse of this rank: one kernel per rank and step,
-                                 the exchange overlaps the streaming */
+                                 rank's receive area peer_out[p] (gqa_sequence_exchange_bytes(),
+                                 zero-filled once when created) as they are produced, every value
+                                 as an 8-byte word {float, epoch}: the data is its own arrival
+                                 flag (peer_flags is not used).  At its end every CTA merges its
+                                 share of the rows (LSE-weighted, the reference's reduce_partials
+                                 algebra, gqa_decode/gqa_decode.py:661-669, across ranks) into
+                                 args->out / out_f32 / out_lse of this rank, waiting - bounded,
+                                 status bit 16 - for words that have not landed: one kernel per
+                                 rank and step, the exchange overlaps the streaming */
 typedef struct gqa_gather_args {
   void* const* peer_out;
   uint32_t* const* peer_flags;
@@ -267,6 +276,11 @@ typedef struct gqa_gather_args {
   int32_t mode;               /* GQA_GATHER_* */
 } gqa_gather_args_t;
 int gqa_decode_attention_gather(const gqa_decode_args_t* args, const gqa_gather_args_t* gather);
+
+/* Bytes of one rank's receive area for GQA_GATHER_SEQUENCE (rows = batch * num_q_heads):
+ * 2 parity halves x world source ranks x (rows * head_dim + rows rounded up to even) 8-byte
+ * words. */
+size_t gqa_sequence_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim);
 
 /*
  * Append one token per sequence to E4M3 caches with fixed per-(sequence, head) scales: the

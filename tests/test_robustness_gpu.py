@@ -109,7 +109,8 @@ def test_gather_wait_expires_and_recovers(G, mode):
     if mode == "heads":
         bufs = [torch.zeros(2 * b * world * hq * d, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
     else:
-        bufs = [torch.zeros(2 * world * rows * (d + 1), dtype=torch.float32, device=DEV) for _ in range(world)]
+        nbytes = int(lib.gqa_sequence_exchange_bytes(world, rows, d))
+        bufs = [torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV) for _ in range(world)]
     flags = [torch.zeros(2 * world, dtype=torch.int32, device=DEV) for _ in range(world)]
     arr = ctypes.c_void_p * world
     ga = _native.GatherArgs()
@@ -135,8 +136,14 @@ def test_gather_wait_expires_and_recovers(G, mode):
     assert st.value == WAIT_EXCHANGE
     if mode == "sequence":
         assert bool((out == 5.0).all()), "no merge may run when a peer's partial never arrived"
-    # this rank's flag was raised on the stand-in peer
-    assert int(flags[1][world * 1 + 0].item()) == 1  # [parity 1][rank 0] = epoch 1
+    if mode == "heads":
+        # this rank's flag was raised on the stand-in peer: [parity 1][rank 0] = epoch 1
+        assert int(flags[1][world * 1 + 0].item()) == 1
+    else:
+        # this rank's rows reached the stand-in peer, every word tagged with epoch 1
+        slot = rows * d + ((rows + 1) & ~1)
+        words = bufs[1].view(torch.int32).view(-1, 2)[(1 * world + 0) * slot:(1 * world + 0) * slot + rows * d + rows]
+        assert bool((words[:, 1] == 1).all())
     # recovery: zero the workspace, then an ordinary launch on it is correct
     assert lib.gqa_decode_workspace_reset(ws.data_ptr(), ws.numel(), None) == 0
     got = G.gqa_decode_attention_batched(qd, kd, vd, None, workspace=ws)
