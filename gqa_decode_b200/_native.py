@@ -21,7 +21,7 @@ FLAG_WORK_STEALING = 8
 FLAG_CLEAR_WORKSPACE = 16
 FLAG_DEPENDENT_LAUNCH = 32
 FLAG_TICKET_MERGE = 64
-TIMESTAMP_WORDS = 8  # uint64 words per CTA in DecodeArgs.debug_timestamps
+TIMESTAMP_WORDS = 12  # uint64 words per CTA in DecodeArgs.debug_timestamps
 STATIC_SCRATCH_BYTES = 16 << 20  # GQA_STATIC_SCRATCH_BYTES
 
 ERRORS = {
@@ -30,6 +30,7 @@ ERRORS = {
     -3: "workspace too small",
     -4: "cuTensorMapEncodeTiled unavailable or failed",
     -5: "size beyond a documented maximum",
+    -6: "internal self-check failed",
 }
 
 

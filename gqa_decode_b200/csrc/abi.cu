@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 #include "decode_kernel.cuh"
 #include "fp8_path.cuh"
@@ -111,6 +112,7 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long lon
 // Cost units charged per group by the balanced partition: starting and finishing a group
 // costs about 1.5 us, i.e. two 32 KB tiles of streaming or one 64 KB tile.
 static int group_overhead_for(int head_dim, int kv_dtype) {
+  if (const char* e = getenv("GQA_GROUP_OVERHEAD")) return atoi(e);
   return (kv_dtype == GQA_DTYPE_E4M3 || head_dim == 256) ? 1 : 2;
 }
 
@@ -242,12 +244,18 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const int overhead = group_overhead_for(D, a->kv_dtype);
   const long long tiles_per_group = ((long long)a->max_seq_len + tile - 1) / tile + overhead;
 
-  // Partial slots: explicit splits need exactly groups*K; the balanced schedule takes what
-  // the workspace offers and sizes its chunks accordingly.
+  // Partial slots: explicit splits need exactly groups*K; static balanced ranges one per group
+  // and CTA (units are dealt one by one: equal shares to within a unit); with work stealing
+  // the schedule takes what the workspace offers and sizes its chunks accordingly.
+  const bool steal = fused && splits == 0 && (a->flags & GQA_FLAG_WORK_STEALING);
   WorkspaceLayout w;
   int chunk = 1;
   if (splits > 0) {
     w = layout_workspace(groups, num_ctas, groups * splits, G, D);
+    if (a->workspace_bytes < w.total) return GQA_ERR_WORKSPACE;
+  } else if (!steal) {
+    const long long slots = groups + num_ctas + 2;
+    w = layout_workspace(groups, num_ctas, slots, G, D);
     if (a->workspace_bytes < w.total) return GQA_ERR_WORKSPACE;
   } else {
     long long slots = slots_that_fit(groups, num_ctas, G, D, a->workspace_bytes);
@@ -298,7 +306,9 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   prm.sched.chunk_tiles = chunk;
   prm.sched.group_overhead = overhead;
   // stealing needs the in-kernel merge (partials are counted as they complete)
-  prm.sched.steal = (fused && splits == 0 && (a->flags & GQA_FLAG_WORK_STEALING)) ? 1 : 0;
+  prm.sched.steal = steal ? 1 : 0;
+  // uniform lengths on the static balanced schedule: geometry and reciprocals from the host
+  prepare_fast_schedule(prm.sched);
   prm.num_q_heads = a->num_q_heads;
   prm.group = G;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)D);
@@ -477,12 +487,8 @@ __global__ void schedule_dump_kernel(SchedParams sp, long long* records, long lo
 }
 
 constexpr int kDumpOverhead = 2;  // group overhead units used by the schedule dumps
-static int default_chunk(int batch, int num_kv_heads, int max_seq_len, int tile_rows, int num_ctas) {
-  const long long groups = (long long)batch * num_kv_heads;
-  return choose_chunk_tiles(groups,
-                            ((long long)max_seq_len + tile_rows - 1) / tile_rows + kDumpOverhead,
-                            num_ctas, default_balanced_slots(groups, num_ctas));
-}
+// the dumps replay the static schedule: one unit per chunk
+static int default_chunk(int, int, int, int, int) { return 1; }
 
 }  // namespace gqa
 
@@ -592,9 +598,12 @@ int gqa_decode_attention_static_scratch(const gqa_decode_args_t* args) {
   if (ctas <= 0) return (int)cudaErrorNoDevice;
   const long long groups = (long long)args->batch * args->num_kv_heads;
   const int G = args->num_q_heads / args->num_kv_heads;
-  // Explicit splits need groups*K partial slots, the balanced schedule at least one per
-  // group (its chunk size adapts to the room there is): refuse what cannot fit the array.
-  const long long need_slots = args->num_splits > 0 ? groups * args->num_splits : groups + 2;
+  // Explicit splits need groups*K partial slots, the balanced schedule one per group and CTA
+  // (with work stealing at least one per group: its chunk size adapts to the room there is):
+  // refuse what cannot fit the array.
+  const long long need_slots = args->num_splits > 0 ? groups * args->num_splits
+                               : (args->flags & GQA_FLAG_WORK_STEALING) ? groups + 2
+                                                                        : groups + ctas + 2;
   const WorkspaceLayout w = layout_workspace(groups, ctas, need_slots, G, args->head_dim);
   if (w.total + 512 > (size_t)GQA_STATIC_SCRATCH_BYTES) return GQA_ERR_LIMIT;
   // The array still holds the previous call's bytes: deques, tickets and status must start
@@ -770,6 +779,10 @@ int64_t gqa_schedule_dump(const int32_t* seq_lens_host, int32_t batch, int32_t n
   SchedParams sp{seq_lens_host, batch,      num_kv_heads, max_seq_len, tile_rows,
                  num_ctas,      num_splits, kv_layout,
                  default_chunk(batch, num_kv_heads, max_seq_len, tile_rows, num_ctas), kDumpOverhead, 0};
+  // Where the closed-form set-up applies (uniform lengths), the replay runs twice - general
+  // path and closed form - and the two must agree segment for segment.
+  SchedParams sp_fast = sp;
+  prepare_fast_schedule(sp_fast);
   int64_t n = 0;
   for (int c = 0; c < num_ctas; ++c) {
     Walker wk;
@@ -787,6 +800,26 @@ int64_t gqa_schedule_dump(const int32_t* seq_lens_host, int32_t batch, int32_t n
     else wk2.seek_serial(t0);
     Segment* all = got <= kDumpSegs ? buf : new Segment[got];
     wk2.walk_static(c, t0, t1, all, got);
+    if (sp_fast.fast) {
+      Walker wf;
+      wf.init_serial(sp_fast);
+      long long f0, f1;
+      if (!wf.static_range(c, f0, f1) || f0 != t0 || f1 != t1) return GQA_ERR_INTERNAL;
+      wf.seek_serial(f0);
+      Segment* again = new Segment[got > 0 ? got : 1];
+      const long long got2 = wf.walk_static(c, f0, f1, again, got);
+      bool same = got2 == got;
+      for (long long i = 0; same && i < got; ++i)
+        same = again[i].b == all[i].b && again[i].h == all[i].h && again[i].len == all[i].len &&
+               again[i].row_begin == all[i].row_begin && again[i].row_end == all[i].row_end &&
+               again[i].kv_row0 == all[i].kv_row0 && again[i].slot == all[i].slot &&
+               again[i].first_slot == all[i].first_slot && again[i].n_parts == all[i].n_parts;
+      delete[] again;
+      if (!same) {
+        if (all != buf) delete[] all;
+        return GQA_ERR_INTERNAL;
+      }
+    }
     for (long long i = 0; i < got; ++i, ++n)
       if (n < capacity) put_record(reinterpret_cast<long long*>(records) + 9 * n, c, all[i]);
     if (all != buf) delete[] all;
@@ -804,6 +837,7 @@ int gqa_schedule_dump_device(const int32_t* seq_lens, int32_t batch, int32_t num
   SchedParams sp{seq_lens, batch,      num_kv_heads, max_seq_len, tile_rows,
                  num_ctas, num_splits, kv_layout,
                  default_chunk(batch, num_kv_heads, max_seq_len, tile_rows, num_ctas), kDumpOverhead, 0};
+  prepare_fast_schedule(sp);  // uniform lengths: the device takes the closed-form set-up
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int64_t), st);
   if (e != cudaSuccess) return (int)e;

@@ -29,7 +29,7 @@ constexpr int kMergeThreads = 128;  // block size of the stand-alone merge kerne
 constexpr int kMaxStages = 8;
 constexpr int kMaxPeers = 8;  // GPUs of one NVLink domain that can gather head-sharded outputs
 constexpr int kDescRing = 32;  // tile descriptors kept in shared memory (>= 4 * kMaxStages)
-constexpr int kTimestampWords = 8;  // diagnostics words per CTA (DecodeParams::timestamps)
+constexpr int kTimestampWords = 12;  // diagnostics words per CTA (DecodeParams::timestamps)
 constexpr int kDeferCap = 4;  // group merges a CTA puts off until its streaming is over (one is the rule)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -76,7 +76,9 @@ struct DecodeParams {
                                    // {prologue done, first load issued, first tile landed, start of
                                    // the last segment's epilogue, end, ticket drawn by the CTA's
                                    // last merging segment (0: it merged nothing), SM id, tile
-                                   // descriptors consumed}; builds with
+                                   // descriptors consumed, then for the CTA's last polled merge
+                                   // {log-sum-exps all there, thread 0's outputs fetched, thread 0's
+                                   // row stored, 0}}; builds with
                                    // GQA_PROFILE_WAITS append, after those words of the whole grid,
                                    // per CTA {producer wait cycles, producer cycles, tiles posted,
                                    // consumer warp 0 wait-for-data cycles, consumer cycles}
@@ -603,13 +605,18 @@ __device__ __noinline__ void merge_group_wide(const DecodeParams* __restrict__ p
 __device__ __forceinline__ float not_zero(float v) {
   return __float_as_uint(v) == 0u ? __uint_as_float(0x80000000u) : v;  // +0 -> -0
 }
-__device__ __forceinline__ float4 ld_volatile_f4(const float* p) {
-  const uint4 v = ld_volatile_v4(p);
-  return make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+// Loads for polling: served by L2 (where other SMs' stores become visible), issued every time
+// the statement is reached (the compiler may neither hoist nor merge them), and - unlike
+// ld.volatile - ordinary weak loads to the hardware, so that dozens of them overlap.
+__device__ __forceinline__ float4 ld_poll_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
 }
-__device__ __forceinline__ float ld_volatile_f1(const float* p) {
+__device__ __forceinline__ float ld_poll_f1(const float* p) {
   float v;
-  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
   return v;
 }
 
@@ -632,7 +639,7 @@ __device__ __forceinline__ void merge_polled_body(const DecodeParams& prm, int f
   for (int i = tid; i < n * G; i += nthreads) {
     const unsigned long long t0 = global_timer_ns();
     unsigned pause = 64;
-    while (__float_as_uint(ld_volatile_f1(lse_g + i)) == 0u) {
+    while (__float_as_uint(ld_poll_f1(lse_g + i)) == 0u) {
       if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // reported by the fetch below
       __nanosleep(pause);
       if (pause < 512) pause *= 2;
@@ -656,8 +663,8 @@ __device__ __forceinline__ void merge_polled_body(const DecodeParams& prm, int f
 #pragma unroll
         for (int u = 0; u < kMergeWide; ++u) {
           if ((pending >> u) & 1u) {
-            l[u] = ld_volatile_f1(lse_g + (size_t)(p0 + u) * G + row);
-            o[u] = ld_volatile_f4(o_g + (size_t)(p0 + u) * o_step);
+            l[u] = ld_poll_f1(lse_g + (size_t)(p0 + u) * G + row);
+            o[u] = ld_poll_f4(o_g + (size_t)(p0 + u) * o_step);
           }
         }
 #pragma unroll
@@ -720,14 +727,119 @@ __device__ __forceinline__ void merge_polled_body(const DecodeParams& prm, int f
     }
   }
 }
-// The merge as it runs after a CTA's streaming: out of line, so that its hundred-odd live
-// registers (kMergeWide partials per thread in flight) do not weigh on the register
-// allocation of the streaming loop; the launch parameters are reached through their address
-// in the parameter space.
+// The polled merge as it runs after a CTA's streaming, when the pipeline stages in shared
+// memory are free: a thread copies its four columns and the log-sum-exp of every partial
+// straight into shared memory with cp.async (no destination registers, so a short rolled loop
+// puts dozens of copies in flight), waits once, and folds them together from shared memory.
+// Code executed once per launch is cold in the instruction cache: two small loops cost a
+// fraction of what an unrolled register version costs, and they need next to no registers.
+// `stage` is 16-byte aligned scratch of `stage_bytes` bytes, private to the calling threads.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
 template <typename Q, int D>
-__device__ __noinline__ void merge_group_polled(const DecodeParams* __restrict__ prmp, int first_slot,
-                                                int n, long long out_row0, int tid, int nthreads) {
-  merge_polled_body<Q, D, kMergeWide>(*prmp, first_slot, n, out_row0, tid, nthreads);
+__device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int first_slot, int n,
+                                                    long long out_row0, int tid, int nthreads,
+                                                    uint8_t* stage, int stage_bytes) {
+  const int G = prm.group;
+  constexpr int D4 = D / 4;
+  float* lse_g = prm.part_lse + (size_t)first_slot * G;
+  // wait quietly until every log-sum-exp is there (see merge_polled_body)
+  for (int i = tid; i < n * G; i += nthreads) {
+    const unsigned long long t0 = global_timer_ns();
+    unsigned pause = 64;
+    while (__float_as_uint(ld_poll_f1(lse_g + i)) == 0u) {
+      if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // reported by the fetch below
+      __nanosleep(pause);
+      if (pause < 512) pause *= 2;
+    }
+  }
+  bar_sync(1, nthreads);
+  if (prm.timestamps && tid == 0) prm.timestamps[kTimestampWords * blockIdx.x + 8] = global_timer_ns();
+  int cap = stage_bytes / (nthreads * 20);  // partials per batch: 16 + 4 bytes per thread each
+  if (cap > 64) cap = 64;
+  float4* my_o = reinterpret_cast<float4*>(stage) + tid;                             // [cap][nthreads]
+  float* my_l = reinterpret_cast<float*>(stage + (size_t)cap * nthreads * 16) + tid;  // [cap][nthreads]
+  const uint32_t my_o_addr = smem_u32(my_o), my_l_addr = smem_u32(my_l);
+  const size_t o_step = (size_t)G * D;  // floats between consecutive partials
+  for (int idx = tid; idx < G * D4; idx += nthreads) {
+    const int row = idx / D4, d4 = idx % D4;
+    float* o_g = prm.part_o + ((size_t)first_slot * G + row) * D + 4 * d4;
+    float mx = -INFINITY, wsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool complete = true;
+    for (int p0 = 0; p0 < n && complete; p0 += cap) {
+      const int nb = n - p0 < cap ? n - p0 : cap;
+      const unsigned long long t0 = global_timer_ns();
+      for (;;) {
+        for (int p = 0; p < nb; ++p) {
+          cp_async_16(my_o_addr + (uint32_t)p * nthreads * 16, o_g + (size_t)(p0 + p) * o_step);
+          cp_async_4(my_l_addr + (uint32_t)p * nthreads * 4, lse_g + (size_t)(p0 + p) * G + row);
+        }
+        cp_async_wait_all();
+        bool all_there = true;
+        for (int p = 0; p < nb; ++p) {
+          const float4 o = my_o[p * nthreads];
+          all_there = all_there && __float_as_uint(my_l[p * nthreads]) != 0u &&
+                      __float_as_uint(o.x) != 0u && __float_as_uint(o.y) != 0u &&
+                      __float_as_uint(o.z) != 0u && __float_as_uint(o.w) != 0u;
+        }
+        if (all_there) break;
+        if (global_timer_ns() - t0 > prm.wait_limit_ns) {
+          atomicOr(prm.status, kStatusWaitPartial);
+          complete = false;
+          break;
+        }
+        __nanosleep(200);
+      }
+      if (!complete) break;
+      if (prm.timestamps && tid == 0 && idx == 0) prm.timestamps[kTimestampWords * blockIdx.x + 9] = global_timer_ns();
+      // running maximum across batches (one batch is the rule)
+      float bm = -INFINITY;
+      for (int p = 0; p < nb; ++p) bm = fmaxf(bm, my_l[p * nthreads]);
+      const float mnew = fmaxf(mx, bm);
+      const float ms = (mnew == -INFINITY) ? 0.f : mnew;
+      if (p0 > 0) {
+        const float keep = fast_exp2((mx - ms) * kLog2e);
+        acc.x *= keep;
+        acc.y *= keep;
+        acc.z *= keep;
+        acc.w *= keep;
+        wsum *= keep;
+      }
+      mx = mnew;
+      for (int p = 0; p < nb; ++p) {
+        const float w = fast_exp2((my_l[p * nthreads] - ms) * kLog2e);
+        const float4 o = my_o[p * nthreads];
+        acc.x += w * o.x;
+        acc.y += w * o.y;
+        acc.z += w * o.z;
+        acc.w += w * o.w;
+        wsum += w;
+      }
+    }
+    if (!complete) continue;
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    acc.x *= inv;
+    acc.y *= inv;
+    acc.z *= inv;
+    acc.w *= inv;
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    store_final<Q, D>(prm, out_row0 + row, d4, acc);
+    if (d4 == 0)
+      store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
+    if (prm.timestamps && tid == 0 && idx == 0) prm.timestamps[kTimestampWords * blockIdx.x + 10] = global_timer_ns();
+    for (int p = 0; p < n; ++p) {
+      *reinterpret_cast<float4*>(o_g + (size_t)p * o_step) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (d4 == 0) lse_g[(size_t)p * G + row] = 0.f;
+    }
+  }
 }
 
 // Sequence shards, end of the kernel: LSE-weighted merge of the `world` partials of this CTA's
@@ -1228,7 +1340,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             continue;
           }
           const int gi = wk.b * Hkv + wk.h;
-          const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           if (gi != cached_group) {
             // per-group values are computed once per group
             cached_group = gi;
@@ -1236,16 +1347,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             d.h = wk.h;
             d.ntg = wk.ntg;
             row0 = wk.kv_row0();
-            // The slot fields take four divisions - a microsecond or two of dependent integer
-            // code on one thread - and the consumers read them at the end of a segment only:
-            // unless this tile already ends the segment, it is sent on its way first.
-            const bool early = !last;
-            if (early) {
-              d.valid = min(TILE, wk.len - wk.ti * TILE);
-              d.flags = (open ? 0 : kTileFirst) | kTileShared;
-              if (paged) pr.post_paged(d, wk.ti * TILE);
-              else pr.post(d, row0 + (long long)wk.ti * TILE);
-            }
             if (prm.sched.steal) {
               d.first_slot = wk.group_first_slot();
               d.slot = -1;
@@ -1255,12 +1356,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               wk.group_static_slots(cta, d.first_slot, d.n_parts, index);
               d.slot = d.first_slot + index;
             }
-            if (early) {
-              open = true;
-              wk.advance();
-              continue;
-            }
           }
+          const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           d.valid = min(TILE, wk.len - wk.ti * TILE);
           d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0) | kTileShared;
           if (paged) pr.post_paged(d, wk.ti * TILE);
@@ -1559,9 +1656,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     for (int e = 0; e < todo; ++e) {
       const int first_slot = sm_defer_list[3 * e], n = sm_defer_list[3 * e + 1];
       const long long row0 = sm_defer_list[3 * e + 2];
-      // (out of line except in the E4M3 kernels, whose consumers have no registers to spare)
-      if (Tr::kFp8) merge_polled_body<Q, D, 8>(prm, first_slot, n, row0, tid, kConsumerThreads);
-      else merge_group_polled<Q, D>(&prm, first_slot, n, row0, tid, kConsumerThreads);
+      // (the streaming loop is over and every tile has been consumed: the pipeline stages
+      // serve as staging memory)
+      merge_polled_staged<Q, D>(prm, first_slot, n, row0, tid, kConsumerThreads, stage0,
+                                nst * Tr::kStageBytes);
     }
   }
 

@@ -9,7 +9,8 @@
 // one-tile groups twice the work of its neighbours.  The line is therefore measured in
 // units; a unit is either a tile or a slice of a group's overhead.
 //
-//   balanced (num_splits == 0): the line is cut into M chunks of `chunk_tiles` tiles and
+//   balanced (num_splits == 0): the line is cut into M chunks of `chunk_tiles` units (one
+//     unit per chunk unless CTAs steal work from each other: equal shares to within a unit) and
 //     CTA c owns the chunk range [c*M/P, (c+1)*M/P), P = min(#CTAs, M).  A CTA works
 //     through its own range from the front; consecutive chunks fuse into one running
 //     segment, so an undisturbed CTA produces one partial per group it touches, exactly
@@ -28,8 +29,9 @@
 //
 // A "segment" is a run of tiles of one group processed by one CTA without interruption;
 // it produces one partial (normalised O, log-sum-exp).  Partial slots of a group start at
-// first_slot = (chunk of the group's first tile) + group index: both terms grow along the
-// line, so groups get disjoint slot ranges with room for one partial per chunk.
+// first_slot = (first CTA holding a tile of the group, or with stealing the chunk of the
+// group's first tile) + group index: both terms grow along the line, so groups get disjoint
+// slot ranges with room for one partial per CTA (per chunk).
 #pragma once
 #include <stdint.h>
 
@@ -56,6 +58,25 @@ GQA_HD long long imod(long long a, long long b) {
   return a % b;
 }
 
+// Division by a divisor known on the host: multiply-shift reciprocal (Granlund-Montgomery),
+// exact for every 32-bit numerator.  Three instructions instead of a division routine.
+struct FastDiv {
+  unsigned mul, s1, s2;
+};
+GQA_HD unsigned fdiv(unsigned n, const FastDiv& f) {
+  const unsigned t = (unsigned)(((unsigned long long)f.mul * n) >> 32);
+  return (t + ((n - t) >> f.s1)) >> f.s2;
+}
+inline FastDiv make_fastdiv(unsigned d) {
+  unsigned l = 0;
+  while ((1ull << l) < d) ++l;
+  FastDiv f;
+  f.mul = (unsigned)((((1ull << l) - d) << 32) / d + 1);
+  f.s1 = l < 1 ? l : 1;
+  f.s2 = l < 1 ? 0 : l - 1;
+  return f;
+}
+
 enum KvLayout : int {
   kLayoutPadded = 0,  // K/V [batch, Hkv, max_seq, D]: head slab of (b,h) starts at row (b*Hkv+h)*max_seq
   kLayoutPacked = 1,  // K/V [sum_b Hkv*len_b, D]: sequence b holds [Hkv, len_b, D] after all earlier sequences
@@ -76,6 +97,16 @@ struct SchedParams {
   int group_overhead;  // balanced: cost units charged per (sequence, KV head) group
   int steal;        // balanced: 1 = idle CTAs steal chunks (results then depend on timing in
                     // the last float32 bits), 0 = static ranges only (bit-reproducible)
+  // Uniform lengths (seq_lens == null), balanced static schedule: the geometry is worked out
+  // on the host, together with reciprocals of the divisors a CTA's set-up needs, so that the
+  // set-up is a few dozen instructions instead of a scan and a dozen divisions.  Every
+  // numerator stays below 2^32 (the host checks).  Same schedule as the general path.
+  int fast;                   // 1: the fields below are valid
+  int fast_parts;             // CTAs that own chunks
+  long long fast_total;       // units in the batch
+  long long fast_chunks;      // chunks
+  FastDiv div_ung, div_hkv, div_chunk, div_chunks, div_parts;  // units per group, KV heads,
+                              // units per chunk, chunks, owning CTAs
 };
 
 // One run of tiles inside one group, as reported by the host-side replay of the static
@@ -145,20 +176,53 @@ struct Walker {
     parts = n_chunks < p.num_ctas ? n_chunks : p.num_ctas;
   }
   GQA_HD long long chunk_tiles() const { return p.chunk_tiles > 0 ? p.chunk_tiles : 1; }
+  // host-prepared geometry (SchedParams::fast)
+  GQA_HD void set_geometry_fast() {
+    total = p.fast_total;
+    n_chunks = p.fast_chunks;
+    parts = p.fast_parts;
+    sb = 0;
+    s_tiles_before = s_rows_before = 0;
+    b = h = ui = ti = len = ntg = 0;
+    tiles_before_group = rows_before_seq = 0;
+    unit = 0;
+  }
+  // position on unit t0 in closed form (uniform lengths)
+  GQA_HD void seat_fast(long long t0) {
+    len = p.max_seq;
+    ntg = tiles_of(len);
+    const int ung = ntg + overhead();
+    const unsigned gi = fdiv((unsigned)t0, p.div_ung);
+    ui = (int)((unsigned)t0 - gi * (unsigned)ung);
+    ti = ui - overhead();
+    b = (int)fdiv(gi, p.div_hkv);
+    h = (int)(gi - (unsigned)b * (unsigned)p.num_kv_heads);
+    tiles_before_group = (long long)gi * ung;
+    rows_before_seq = (long long)b * len;
+    sb = b;
+    s_tiles_before = (long long)b * p.num_kv_heads * ung;
+    s_rows_before = rows_before_seq;
+  }
   // chunk (balanced) or unit (explicit) range owned by CTA c
   GQA_HD void cta_range(int c, long long& q0, long long& q1) const {
     if (p.num_splits > 0) {
       q0 = idiv(c * total, p.num_ctas);
       q1 = idiv((c + 1) * total, p.num_ctas);
     } else if (c < parts) {
-      q0 = idiv(c * n_chunks, parts);
-      q1 = idiv((c + 1) * n_chunks, parts);
+      if (p.fast) {
+        q0 = fdiv((unsigned)(c * n_chunks), p.div_parts);
+        q1 = fdiv((unsigned)((c + 1) * n_chunks), p.div_parts);
+      } else {
+        q0 = idiv(c * n_chunks, parts);
+        q1 = idiv((c + 1) * n_chunks, parts);
+      }
     } else {
       q0 = q1 = 0;
     }
   }
   // owner of chunk q: largest c with floor(c*M/P) <= q (P <= M: every owner has chunks)
   GQA_HD long long cta_of_chunk(long long q) const {
+    if (p.fast) return fdiv((unsigned)((q + 1) * parts - 1), p.div_chunks);
     return idiv((q + 1) * parts - 1, n_chunks);
   }
   GQA_HD void chunk_tile_range(long long q, long long& t0, long long& t1) const {
@@ -176,25 +240,33 @@ struct Walker {
   // (measured from the group's first tile unit: chunks that only hold its overhead produce
   // no partial)
   GQA_HD long long group_first_tile_unit() const { return tiles_before_group + overhead(); }
+  // chunk that holds unit u
+  GQA_HD long long chunk_of(long long u) const {
+    return p.fast ? (long long)fdiv((unsigned)u, p.div_chunk) : idiv(u, chunk_tiles());
+  }
+  // Static ranges: a group's partials are numbered from (first CTA that holds a tile of it) +
+  // (group index) - both grow along the line and a group has one partial per CTA it spans, so
+  // the ranges are disjoint and groups + CTAs slots are enough.  Stealing: any chunk may end
+  // up a partial of its own, so the numbering starts from the chunk of the group's first tile.
   GQA_HD int group_first_slot() const {
-    return (int)(idiv(group_first_tile_unit(), chunk_tiles()) + group_index());
+    const long long q = chunk_of(group_first_tile_unit());
+    return (int)((p.steal ? q : cta_of_chunk(q)) + group_index());
   }
   GQA_HD int group_static_parts() const {
-    const long long c = chunk_tiles();
-    return (int)(cta_of_chunk(idiv(group_first_tile_unit() + ntg - 1, c)) -
-                 cta_of_chunk(idiv(group_first_tile_unit(), c)) + 1);
+    return (int)(cta_of_chunk(chunk_of(group_first_tile_unit() + ntg - 1)) -
+                 cta_of_chunk(chunk_of(group_first_tile_unit())) + 1);
   }
   GQA_HD int group_static_index(int cta) const {
-    return (int)(cta - cta_of_chunk(idiv(group_first_tile_unit(), chunk_tiles())));
+    return (int)(cta - cta_of_chunk(chunk_of(group_first_tile_unit())));
   }
   // The three values above in one go (four divisions instead of seven): first slot of the
   // current group, how many partials the static schedule makes of it, and which of them CTA
   // `cta` writes.
   GQA_HD void group_static_slots(int cta, int& first_slot, int& n_parts, int& index) const {
-    const long long c = chunk_tiles(), u0 = group_first_tile_unit();
-    const long long q_first = idiv(u0, c), q_last = idiv(u0 + ntg - 1, c);
+    const long long u0 = group_first_tile_unit();
+    const long long q_first = chunk_of(u0), q_last = chunk_of(u0 + ntg - 1);
     const long long c_first = cta_of_chunk(q_first), c_last = cta_of_chunk(q_last);
-    first_slot = (int)(q_first + group_index());
+    first_slot = (int)(c_first + group_index());  // static ranges only, see group_first_slot()
     n_parts = (int)(c_last - c_first + 1);
     index = (int)(cta - c_first);
   }
@@ -246,6 +318,10 @@ struct Walker {
   // Serial versions: usable from host code or from a single device thread.
   GQA_HD void init_serial(const SchedParams& sp) {
     p = sp;
+    if (p.fast) {
+      set_geometry_fast();
+      return;
+    }
     if (p.num_splits > 0) {
       set_geometry((long long)p.batch * p.num_kv_heads * p.num_splits);
       return;
@@ -255,6 +331,10 @@ struct Walker {
     set_geometry(n * p.num_kv_heads);
   }
   GQA_HD void seek_serial(long long t0) {
+    if (p.fast) {
+      seat_fast(t0);
+      return;
+    }
     rewind_if_behind(t0);
     for (; sb < p.batch; ++sb) {
       const int l = len_of(sb);
@@ -279,6 +359,10 @@ struct Walker {
   // identical state.  Lengths are read 32 at a time and combined with shuffles.
   __device__ __forceinline__ void init_warp(const SchedParams& sp) {
     p = sp;
+    if (p.fast) {
+      set_geometry_fast();
+      return;
+    }
     if (p.num_splits > 0) {
       set_geometry((long long)p.batch * p.num_kv_heads * p.num_splits);
       return;
@@ -290,6 +374,10 @@ struct Walker {
     set_geometry(n * p.num_kv_heads);
   }
   __device__ __forceinline__ void seek_warp(long long t0) {
+    if (p.fast) {
+      seat_fast(t0);
+      return;
+    }
     const int lane = threadIdx.x & 31;
     const unsigned full = 0xffffffffu;
     rewind_if_behind(t0);
@@ -424,6 +512,30 @@ struct Walker {
     return n;
   }
 };
+
+// Host side: fill in SchedParams::fast and what goes with it where the closed-form set-up
+// applies (uniform lengths, balanced static schedule, every numerator below 2^32).
+inline void prepare_fast_schedule(SchedParams& sp) {
+  sp.fast = 0;
+  if (sp.seq_lens || sp.num_splits > 0 || sp.steal || sp.batch <= 0 || sp.num_kv_heads <= 0 ||
+      sp.max_seq <= 0 || sp.tile_rows <= 0 || sp.num_ctas <= 0)
+    return;
+  const long long tiles = ((long long)sp.max_seq + sp.tile_rows - 1) / sp.tile_rows;
+  const long long ung = tiles + sp.group_overhead;
+  const long long total = (long long)sp.batch * sp.num_kv_heads * ung;
+  const long long chunk = sp.chunk_tiles > 0 ? sp.chunk_tiles : 1;
+  if (total * ((long long)sp.num_ctas + 1) >= (1ll << 31)) return;
+  const long long chunks = (total + chunk - 1) / chunk;
+  sp.fast = 1;
+  sp.fast_total = total;
+  sp.fast_chunks = chunks;
+  sp.fast_parts = (int)(chunks < sp.num_ctas ? chunks : sp.num_ctas);
+  sp.div_ung = make_fastdiv((unsigned)ung);
+  sp.div_hkv = make_fastdiv((unsigned)sp.num_kv_heads);
+  sp.div_chunk = make_fastdiv((unsigned)chunk);
+  sp.div_chunks = make_fastdiv((unsigned)chunks);
+  sp.div_parts = make_fastdiv((unsigned)sp.fast_parts);
+}
 
 // Upper bound on partial slots for a launch with chunk size `chunk_tiles`:
 // one slot per chunk plus one per group.

@@ -72,6 +72,7 @@ extern "C" {
 #define GQA_ERR_WORKSPACE (-3) /* workspace too small */
 #define GQA_ERR_DRIVER (-4)    /* cuTensorMapEncodeTiled unavailable or failed */
 #define GQA_ERR_LIMIT (-5)     /* size beyond a documented maximum */
+#define GQA_ERR_INTERNAL (-6)  /* a self-check of the library failed (please report) */
 
 /*
  * One decode step over a batch.  Replaces the argument lists of
@@ -112,11 +113,11 @@ typedef struct gqa_decode_args {
   uint64_t wait_limit_ns;      /* bound on every wait inside the kernel (a tile that never lands,
                                   a peer GPU's flag); on expiry a status bit is set and the
                                   kernel returns.  0: two seconds */
-  uint64_t* debug_timestamps;  /* optional diagnostics: device buffer of 8 * num_ctas uint64; per
+  uint64_t* debug_timestamps;  /* optional diagnostics: device buffer of 12 * num_ctas uint64; per
                                   CTA {prologue done, first load issued, first tile landed, start
-                                  of the last segment's epilogue, end, ticket drawn before the
-                                  CTA's last merge or 0} in %globaltimer ns, then {SM id, tiles
-                                  consumed} */
+                                  of the last segment's epilogue, end, start of the CTA's merge
+                                  or 0} in %globaltimer ns, {SM id, tiles consumed}, then three
+                                  more times of that merge and a spare word */
 } gqa_decode_args_t;
 
 /*
@@ -194,9 +195,8 @@ int gqa_decode_attention_persistent(const gqa_decode_args_t* args);
  *
  * Limits and rules:
  *  - if the launch cannot fit the array (explicit splits need batch*Hkv*K partial slots of
- *    G*(D+1)*4 bytes each, the balanced schedule at least batch*Hkv + 2 of them and uses
- *    coarser work chunks when room is short) the call returns GQA_ERR_LIMIT and launches
- *    nothing;
+ *    G*(D+1)*4 bytes each, the balanced schedule batch*Hkv + num_ctas + 2 of them) the call
+ *    returns GQA_ERR_LIMIT and launches nothing;
  *  - the first call on each device looks up the array's device address (once per
  *    device, with that device current); make that first call during set-up, before any
  *    stream capture is begun;

@@ -314,7 +314,7 @@ def test_plan_and_cuda_graph_replay(G):
 
 def test_work_stealing_matches_static_schedule(G):
     """With work_stealing=True idle CTAs steal chunks; the result may differ from the
-    default static schedule only by float32 summation order (far below one bf16 ulp), and
+    default static schedule only by rounding noise far below one bf16 ulp of the output, and
     the static schedule is bit-reproducible."""
     g = torch.Generator().manual_seed(31)
     lens = [9000, 1, 4097, 7, 30000, 64, 12345, 0]
@@ -328,7 +328,9 @@ def test_work_stealing_matches_static_schedule(G):
     assert torch.equal(a, b) and torch.equal(a32, b32)
     for _ in range(5):
         c, c32 = G.gqa_decode_attention_batched(q, k, v, sl, return_f32=True, work_stealing=True)
-        assert float((c32 - a32).abs().max()) < 2e-5 * max(1.0, float(a32.abs().max())), float((c32 - a32).abs().max())
+        # (the two schedules cut the sequences at different places, so the 16-bit rounding of the
+        # softmax weights, taken relative to each piece's running maximum, differs in its noise)
+        assert float((c32 - a32).abs().max()) < 2e-4 * max(1.0, float(a32.abs().max())), float((c32 - a32).abs().max())
         assert G.read_status() == 0
     ref = torch.stack([
         O.attend_one_sequence(q[i].cpu(), k[i, :, :l].cpu(), v[i, :, :l].cpu()) if l

@@ -84,3 +84,40 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "lib_path", lambda: str(tmp_path / "absent.so"))
     with pytest.raises(RuntimeError, match="no non-CUDA fallback"):
         _native.load()
+
+
+def test_workspace_bookkeeping_is_by_identity():
+    """The Python layer decides when a workspace's contents have to be cleared: a tensor it has
+    not seen, a tensor last used with another geometry, never the same tensor with the same
+    geometry; a tensor that was freed is forgotten (a new tensor at the same address is new)."""
+    import gc
+
+    import torch
+
+    from gqa_decode_b200 import gqa_decode as g
+
+    dev = torch.device("cuda", 0)  # only used as a dictionary key here
+    a, b = torch.zeros(16, dtype=torch.uint8), torch.zeros(16, dtype=torch.uint8)
+    geo1, geo2 = (1, 32, 8, 128, 0, 0, (False,) * 4, 16), (2, 32, 8, 128, 0, 0, (False,) * 4, 16)
+    assert g._needs_clear(a, dev, geo1) is True      # unknown contents
+    assert g._needs_clear(a, dev, geo1) is False     # same tensor, same geometry
+    assert g._needs_clear(b, dev, geo1) is True      # another tensor
+    assert g._needs_clear(a, dev, geo2) is True      # geometry changed
+    assert g._needs_clear(a, dev, geo2) is False
+    known = len(g._caller_workspaces)
+    del a
+    gc.collect()
+    assert len(g._caller_workspaces) == known - 1
+
+
+def test_epochs_wrap_without_zero_and_keep_alternating():
+    from gqa_decode_b200.distributed import next_epoch
+
+    e, seen = 0xFFFFFFFD, []
+    for _ in range(6):
+        e = next_epoch(e)
+        seen.append(e)
+    assert seen == [0xFFFFFFFE, 0xFFFFFFFF, 2, 3, 4, 5]
+    assert all(x != 0 and x <= 0xFFFFFFFF for x in seen)
+    assert all((x & 1) != (y & 1) for x, y in zip(seen, seen[1:]))  # the buffer halves keep alternating
+    assert next_epoch(0) == 1

@@ -28,8 +28,9 @@ def check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout):
         assert r0 % tile == 0 and r0 <= r1 <= lens[b]
         assert slot not in slots
         slots.add(slot)
-        tiles = sum(-(-l // tile) for l in lens) * hkv
-        bound = batch * hkv * splits if splits else tiles + batch * hkv + 1
+        # explicit splits: K slots per group; balanced: one per group and CTA (what the library
+        # lays out in the workspace)
+        bound = batch * hkv * splits if splits else ctas + batch * hkv + 1
         assert 0 <= slot < bound
         assert first <= slot < first + nparts
         g = (b, h)
@@ -53,14 +54,15 @@ def check(rec, lens, batch, hkv, max_seq, tile, ctas, splits, layout):
             first, nparts = info[(b, h)]
             assert len(covered[(b, h)]) == nparts
     if not splits:
-        # balanced: CTAs own equal numbers of chunks (+-1) of at most 16 cost units, where a
-        # unit is a tile or one of the 2 overhead units every group carries
+        # balanced: CTAs own equal numbers (+-1) of cost units, where a unit is a tile or one of
+        # the 2 overhead units every group carries (a range may end inside a group's overhead,
+        # which this reconstruction charges to the CTA that holds the group's first tile)
         per = np.zeros(ctas, dtype=np.int64)
         for cta, b, h, r0, r1, *_ in rec:
             per[cta] += -(-(r1 - r0) // tile) + (2 if r0 == 0 else 0)
         used = per[per > 0]
-        assert used.max() - used.min() <= 2 * 16 + 2
-        # slot ranges of different groups are disjoint even if every chunk became a partial
+        assert used.max() - used.min() <= 1 + 2 + 2
+        # slot ranges of different groups are disjoint
         spans = sorted((first, first + nparts) for first, nparts in info.values())
         firsts = sorted(set(first for first, _ in info.values()))
         assert len(firsts) == len(info)
@@ -119,3 +121,25 @@ def test_paged_layouts_share_the_padded_schedule(native_lib, splits):
         assert paged.shape == padded.shape
         assert np.array_equal(paged[:, :8], padded[:, :8])
         assert (paged[:, 8] == 0).all()
+
+
+def test_closed_form_setup_matches_general_path(native_lib):
+    """Uniform batches take a closed-form scheduler set-up (host-prepared geometry and
+    multiply-shift reciprocals).  gqa_schedule_dump replays such a launch both ways and returns
+    an error unless the two agree segment for segment; sweep shapes, tiles and CTA counts."""
+    rng = np.random.default_rng(7)
+    cases = [(1, 8, 16384, 64, 148), (1, 8, 131072, 64, 148), (64, 8, 8192, 64, 148), (64, 1, 8192, 64, 148),
+             (8, 8, 32768, 256, 148), (1, 1, 1, 64, 148), (3, 5, 63, 64, 7), (2, 32, 4096, 128, 132),
+             (300, 8, 777, 64, 148), (1, 8, 16384, 64, 1)]
+    for _ in range(150):
+        cases.append((int(rng.integers(1, 70)), int(rng.integers(1, 33)), int(rng.integers(1, 40000)),
+                      int(rng.choice([64, 128, 256])), int(rng.integers(1, 300))))
+    for batch, hkv, max_seq, tile, ctas in cases:
+        cap = 1 << 18
+        rec = np.zeros((cap, 9), dtype=np.int64)
+        n = native_lib.gqa_schedule_dump(None, batch, hkv, max_seq, tile, ctas, 0, 0, rec.ctypes.data, cap)
+        assert n >= 0, (batch, hkv, max_seq, tile, ctas, n)
+        # and the schedule itself covers every key exactly once
+        keys = sum(int(r[4] - r[3]) for r in rec[:min(n, cap)])
+        if n <= cap:
+            assert keys == batch * hkv * max_seq
