@@ -342,15 +342,19 @@ __device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, 
 __device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
   asm volatile("st.volatile.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
-__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+// Loads for polling words that other SMs or GPUs write: served by L2 (where such stores
+// become visible), issued every time the statement is reached (the compiler may neither hoist
+// nor merge an asm volatile), and ordinary weak loads to the hardware, so that dozens of them
+// overlap.
+__device__ __forceinline__ uint4 ld_poll_v4(const void* p) {
   uint4 v;
-  asm volatile("ld.volatile.global.v4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  asm volatile("ld.global.cg.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+__device__ __forceinline__ uint2 ld_poll_v2(const void* p) {
   uint2 v;
-  asm volatile("ld.volatile.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  asm volatile("ld.global.cg.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
 }
 
@@ -605,9 +609,6 @@ __device__ __noinline__ void merge_group_wide(const DecodeParams* __restrict__ p
 __device__ __forceinline__ float not_zero(float v) {
   return __float_as_uint(v) == 0u ? __uint_as_float(0x80000000u) : v;  // +0 -> -0
 }
-// Loads for polling: served by L2 (where other SMs' stores become visible), issued every time
-// the statement is reached (the compiler may neither hoist nor merge them), and - unlike
-// ld.volatile - ordinary weak loads to the hardware, so that dozens of them overlap.
 __device__ __forceinline__ float4 ld_poll_f4(const float* p) {
   float4 v;
   asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -874,9 +875,9 @@ __device__ __noinline__ void merge_sequence_shards(const DecodeParams* __restric
       for (int s = 0; s < kMaxPeers; ++s) {
         if ((pending >> s) & 1u) {
           const uint2* src = part + (size_t)s * slot;
-          lw[s] = ld_volatile_v2(src + (size_t)rows * D + row);
-          a[s] = ld_volatile_v4(src + (size_t)row * D + 4 * d4);
-          b[s] = ld_volatile_v4(src + (size_t)row * D + 4 * d4 + 2);
+          lw[s] = ld_poll_v2(src + (size_t)rows * D + row);
+          a[s] = ld_poll_v4(src + (size_t)row * D + 4 * d4);
+          b[s] = ld_poll_v4(src + (size_t)row * D + 4 * d4 + 2);
         }
       }
 #pragma unroll

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import threading
 import weakref
 from dataclasses import dataclass
 from typing import Optional
@@ -251,6 +252,7 @@ def gqa_decode_attention_batched(
     _entry: str = "auto",
     _no_merge: bool = False,
     _plan_only: bool = False,
+    _bind_shared_workspace: bool = False,
     _gather=None,
 ):
     """One decode step for a batch of sequences with individual KV lengths.
@@ -382,7 +384,7 @@ def gqa_decode_attention_batched(
                            _device_key(dev)[1])
     if workspace is not None:
         ws = workspace
-    elif _plan_only:
+    elif _plan_only and not _bind_shared_workspace:
         # a plan owns its workspace: fixed geometry, zero from the start, never needs clearing,
         # and nothing another launch does can disturb a captured graph that replays it
         ws = torch.zeros(need, dtype=torch.uint8, device=dev)
@@ -394,6 +396,8 @@ def gqa_decode_attention_batched(
     mode = (bool(separate_merge), bool(_no_merge), bool(work_stealing), bool(ticket_merge))
     geometry = (batch, num_q_heads, num_kv_heads, head_dim, splits, num_ctas, mode, ws_bytes)
     clear = (workspace is not None or not _plan_only) and _needs_clear(ws, dev, geometry)
+    if _bind_shared_workspace:
+        clear = False  # decided call by call (see _single_sequence_call)
     if _gather is not None and _gather.mode == _native.GATHER_HEADS:
         out = None  # final rows go to the gathered buffers of every rank (distributed.HeadGather)
     elif out is None:
@@ -445,7 +449,9 @@ def gqa_decode_attention_batched(
     if _plan_only:
         keep = (q, k_cache, v_cache, seq_lens, k_scale, v_scale, ws, out, out_f32, out_lse, block_table,
                 _gather, _timestamps)
-        return DecodePlan(fn, a, dev, result, keep, ws)
+        plan = DecodePlan(fn, a, dev, result, keep, ws)
+        plan._geometry = geometry
+        return plan
     with torch.cuda.device(dev):
         _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")
     return result
@@ -574,9 +580,53 @@ def gqa_decode_attention(
             num_kv_heads, k_cache.shape[1], cfg.block_seq, cfg.target_blocks_per_sm)
         acc, mx, one = _partials_for_python_reduction(q, k_cache, v_cache, None, None, splits)
         return reduce_partials(acc, mx, one, num_q_heads, splits, head_dim)
-    out = gqa_decode_attention_batched(
-        q.unsqueeze(0), k_cache.unsqueeze(0), v_cache.unsqueeze(0), None, num_splits=num_splits)
-    return out.squeeze(0)
+    return _single_sequence_call(q, k_cache, v_cache, num_splits)
+
+
+# Argument blocks of the drop-in entry, one per (device, dtype, shapes, split count): a decode
+# loop calls it with the same shapes every step, and a kernel of twenty microseconds leaves
+# no room for re-validating and re-filling two dozen struct fields in Python each time.
+# (Per thread: the block is patched in place before every call.)
+_single_calls_tls = threading.local()
+
+
+def _single_sequence_call(q, k_cache, v_cache, num_splits):
+    dev = q.device
+    _single_calls = _single_calls_tls.__dict__.setdefault("blocks", {})
+    key = (dev.index, q.dtype, q.shape, k_cache.shape, num_splits)
+    entry = _single_calls.get(key)
+    if entry is None:
+        # first call with this signature: the general path validates what is left to validate
+        # and allocates the shared workspace; then bind a block for the calls that follow
+        out = gqa_decode_attention_batched(
+            q.unsqueeze(0), k_cache.unsqueeze(0), v_cache.unsqueeze(0), None, num_splits=num_splits)
+        plan = gqa_decode_attention_batched(
+            q.unsqueeze(0), k_cache.unsqueeze(0), v_cache.unsqueeze(0), None, num_splits=num_splits,
+            _plan_only=True, _bind_shared_workspace=True)
+        if len(_single_calls) > 64:
+            _single_calls.clear()
+        _single_calls[key] = (plan._args, plan._ref, plan._fn, plan._geometry)
+        return out.squeeze(0)
+    a, ref, fn, geometry = entry
+    # the shared workspace may have grown or served another geometry since
+    ws_entry = _workspaces.get((dev.type, dev.index))
+    if ws_entry is None or ws_entry[0].data_ptr() != a.workspace:
+        del _single_calls[key]
+        return _single_sequence_call(q, k_cache, v_cache, num_splits)
+    clear = ws_entry[1] is not None and ws_entry[1] != geometry
+    ws_entry[1] = geometry
+    out = torch.empty_like(q)
+    a.q, a.k, a.v, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+    a.flags = _native.FLAG_CLEAR_WORKSPACE if clear else 0
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    if dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            rc = fn(ref)
+    else:
+        rc = fn(ref)
+    if rc:
+        _native.check(rc, "gqa_decode_attention")
+    return out
 
 
 def gqa_decode_attention_persistent(
