@@ -705,6 +705,54 @@ def api_call_cost(wl: Workload, calls: int = 200):
     return {"device_us_per_call": a.elapsed_time(b) / calls * 1e3, "host_us_per_call": host_us, "calls": calls}
 
 
+def quantize_cost(dev, peak: float):
+    """The kernels that produce the E4M3 caches (the step before the path): whole-cache
+    quantisation of one K tensor of config 3's size through gqa_quantize_kv_fp8, and the
+    per-token append of config 5's batch through gqa_quantize_append_fp8.  Algorithmic bytes of
+    the former as its two kernels are written: the amax pass reads 2 B per element, the
+    conversion pass reads 2 B and writes 1 B."""
+    from gqa_decode_b200 import fp8_utils
+
+    heads, s = 64, 32768  # 8 sequences x 8 KV heads of config 3
+    sets = [torch.randn(heads, s, D, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(2)]
+    for x in sets:
+        fp8_utils._quantize_one_cuda(x)
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 10
+    a.record()
+    for i in range(n):
+        fp8_utils._quantize_one_cuda(sets[i % 2])
+    b.record()
+    torch.cuda.synchronize(dev)
+    us = a.elapsed_time(b) / n * 1e3
+    nbytes = 5 * heads * s * D
+    out = {"quantize_kv_fp8": {"us_per_call": us, "elements": heads * s * D, "algorithmic_bytes": nbytes,
+                               "bytes_rule": "2 B read by the amax kernel + 2 B read and 1 B written by the conversion kernel, per element",
+                               "gb_s": nbytes / (us * 1e-6) / 1e9, "frac": nbytes / (us * 1e-6) / 1e9 / peak,
+                               "l2": "two input sets of 537 MB alternated"}}
+    del sets
+    bsz, hkv, smax = 64, 8, 8192
+    kc = torch.zeros(bsz, hkv, smax, D, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    vc = torch.zeros_like(kc)
+    kn = torch.randn(bsz, hkv, D, device=dev).to(torch.bfloat16)
+    vn = torch.randn(bsz, hkv, D, device=dev).to(torch.bfloat16)
+    sc = torch.full((bsz, hkv), 1.0 / 64, device=dev)
+    pos = torch.full((bsz,), 100, dtype=torch.int32, device=dev)
+    for _ in range(3):
+        fp8_utils.append_kv_fp8(kn, vn, kc, vc, sc, sc, pos)
+    torch.cuda.synchronize(dev)
+    n = 50
+    a.record()
+    for i in range(n):
+        fp8_utils.append_kv_fp8(kn, vn, kc, vc, sc, sc, pos)
+    b.record()
+    torch.cuda.synchronize(dev)
+    out["append_kv_fp8"] = {"us_per_call": a.elapsed_time(b) / n * 1e3, "batch": bsz, "num_kv_heads": hkv,
+                            "note": "one new token per sequence; launch-bound (64 KB moved), timed through the Python entry"}
+    return out
+
+
 # ----------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -849,6 +897,11 @@ def main():
                 if dist is not None:
                     raise
             torch.cuda.empty_cache()
+        try:
+            others["fp8_cache_producers"] = quantize_cost(dev, peak)
+        except Exception as e:
+            others["fp8_cache_producers"] = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
 
     if rank == 0:
         ms_per_step = res["ms_per_step"]

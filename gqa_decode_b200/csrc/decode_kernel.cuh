@@ -848,7 +848,8 @@ __device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int
 // one level up).  The partials sit in this rank's receive area as {value, epoch} words; a
 // thread fetches all sources of its (row, 4 columns) at once and fetches again, until a time
 // limit, whatever does not carry this step's epoch yet.  A row whose sources never all arrive
-// is left unwritten and the status word gets kStatusWaitExchange.
+// is left unwritten and the status word gets kStatusWaitExchange.  All `nthreads` threads of
+// named barrier 1 call it together.
 template <typename Q, int D>
 __device__ __noinline__ void merge_sequence_shards(const DecodeParams* __restrict__ prmp, int tid,
                                                    int nthreads) {
@@ -861,6 +862,22 @@ __device__ __noinline__ void merge_sequence_shards(const DecodeParams* __restric
   const uint2* part =
       static_cast<const uint2*>(prm.gather_out[prm.gather_rank]) + (size_t)(e & 1u) * w * slot;
   const long long r0 = rows * blockIdx.x / gridDim.x, r1 = rows * (blockIdx.x + 1) / gridDim.x;
+  // Wait quietly: one thread per (row of this CTA's share, source rank) looks at that row's
+  // log-sum-exp word every few hundred nanoseconds.  (If every thread polled all its words,
+  // two thousand threads would keep L2 busy with tens of loads each per poll - bandwidth the
+  // CTAs that still stream, and whose rows everybody is waiting for, need.)
+  for (long long i = tid; i < (r1 - r0) * w; i += nthreads) {
+    const long long row = r0 + i / w;
+    const uint2* word = part + (size_t)(i % w) * slot + (size_t)rows * D + row;
+    const unsigned long long t0 = global_timer_ns();
+    unsigned pause = 64;
+    while (ld_poll_v2(word).y != e) {
+      if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // reported by the fetch below
+      __nanosleep(pause);
+      if (pause < 512) pause *= 2;
+    }
+  }
+  bar_sync(1, nthreads);
   for (long long idx = r0 * D4 + tid; idx < r1 * D4; idx += nthreads) {
     const long long row = idx / D4;
     const int d4 = (int)(idx % D4);
@@ -895,7 +912,7 @@ __device__ __noinline__ void merge_sequence_shards(const DecodeParams* __restric
         atomicOr(prm.status, kStatusWaitExchange);
         break;
       }
-      __nanosleep(64);
+      __nanosleep(200);
     }
     if (pending) continue;
     float mx = -INFINITY;
