@@ -738,9 +738,6 @@ __device__ __forceinline__ void merge_polled_body(const DecodeParams& prm, int f
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.wait_all;" ::: "memory");
 }
@@ -751,23 +748,27 @@ __device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int
   const int G = prm.group;
   constexpr int D4 = D / 4;
   float* lse_g = prm.part_lse + (size_t)first_slot * G;
-  // wait quietly until every log-sum-exp is there (see merge_polled_body)
+  // Wait quietly until every log-sum-exp is there (see merge_polled_body); the values go into
+  // shared memory for everybody (read from L2 here, never again).
+  float* lse_sm = reinterpret_cast<float*>(stage);  // [n][G]
+  const int lse_bytes = (n * G * 4 + 15) & ~15;
   for (int i = tid; i < n * G; i += nthreads) {
     const unsigned long long t0 = global_timer_ns();
     unsigned pause = 64;
-    while (__float_as_uint(ld_poll_f1(lse_g + i)) == 0u) {
-      if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // reported by the fetch below
+    float v;
+    while (__float_as_uint(v = ld_poll_f1(lse_g + i)) == 0u) {
+      if (global_timer_ns() - t0 > prm.wait_limit_ns) break;  // v stays 0: reported below
       __nanosleep(pause);
       if (pause < 512) pause *= 2;
     }
+    lse_sm[i] = v;
   }
   bar_sync(1, nthreads);
   if (prm.timestamps && tid == 0) prm.timestamps[kTimestampWords * blockIdx.x + 8] = global_timer_ns();
-  int cap = stage_bytes / (nthreads * 20);  // partials per batch: 16 + 4 bytes per thread each
+  int cap = (stage_bytes - lse_bytes) / (nthreads * 16);  // partials per batch: 16 bytes per thread each
   if (cap > 64) cap = 64;
-  float4* my_o = reinterpret_cast<float4*>(stage) + tid;                             // [cap][nthreads]
-  float* my_l = reinterpret_cast<float*>(stage + (size_t)cap * nthreads * 16) + tid;  // [cap][nthreads]
-  const uint32_t my_o_addr = smem_u32(my_o), my_l_addr = smem_u32(my_l);
+  float4* my_o = reinterpret_cast<float4*>(stage + lse_bytes) + tid;  // [cap][nthreads]
+  const uint32_t my_o_addr = smem_u32(my_o);
   const size_t o_step = (size_t)G * D;  // floats between consecutive partials
   for (int idx = tid; idx < G * D4; idx += nthreads) {
     const int row = idx / D4, d4 = idx % D4;
@@ -775,20 +776,24 @@ __device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int
     float mx = -INFINITY, wsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     bool complete = true;
+    for (int p = 0; p < n; ++p) {
+      const float l = lse_sm[p * G + row];
+      complete = complete && __float_as_uint(l) != 0u;
+      mx = fmaxf(mx, l);
+    }
+    if (!complete) atomicOr(prm.status, kStatusWaitPartial);
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
     for (int p0 = 0; p0 < n && complete; p0 += cap) {
       const int nb = n - p0 < cap ? n - p0 : cap;
       const unsigned long long t0 = global_timer_ns();
       for (;;) {
-        for (int p = 0; p < nb; ++p) {
+        for (int p = 0; p < nb; ++p)
           cp_async_16(my_o_addr + (uint32_t)p * nthreads * 16, o_g + (size_t)(p0 + p) * o_step);
-          cp_async_4(my_l_addr + (uint32_t)p * nthreads * 4, lse_g + (size_t)(p0 + p) * G + row);
-        }
         cp_async_wait_all();
         bool all_there = true;
         for (int p = 0; p < nb; ++p) {
           const float4 o = my_o[p * nthreads];
-          all_there = all_there && __float_as_uint(my_l[p * nthreads]) != 0u &&
-                      __float_as_uint(o.x) != 0u && __float_as_uint(o.y) != 0u &&
+          all_there = all_there && __float_as_uint(o.x) != 0u && __float_as_uint(o.y) != 0u &&
                       __float_as_uint(o.z) != 0u && __float_as_uint(o.w) != 0u;
         }
         if (all_there) break;
@@ -801,22 +806,8 @@ __device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int
       }
       if (!complete) break;
       if (prm.timestamps && tid == 0 && idx == 0) prm.timestamps[kTimestampWords * blockIdx.x + 9] = global_timer_ns();
-      // running maximum across batches (one batch is the rule)
-      float bm = -INFINITY;
-      for (int p = 0; p < nb; ++p) bm = fmaxf(bm, my_l[p * nthreads]);
-      const float mnew = fmaxf(mx, bm);
-      const float ms = (mnew == -INFINITY) ? 0.f : mnew;
-      if (p0 > 0) {
-        const float keep = fast_exp2((mx - ms) * kLog2e);
-        acc.x *= keep;
-        acc.y *= keep;
-        acc.z *= keep;
-        acc.w *= keep;
-        wsum *= keep;
-      }
-      mx = mnew;
       for (int p = 0; p < nb; ++p) {
-        const float w = fast_exp2((my_l[p * nthreads] - ms) * kLog2e);
+        const float w = fast_exp2((lse_sm[(p0 + p) * G + row] - ms) * kLog2e);
         const float4 o = my_o[p * nthreads];
         acc.x += w * o.x;
         acc.y += w * o.y;
@@ -831,7 +822,6 @@ __device__ __forceinline__ void merge_polled_staged(const DecodeParams& prm, int
     acc.y *= inv;
     acc.z *= inv;
     acc.w *= inv;
-    const float ms = (mx == -INFINITY) ? 0.f : mx;
     store_final<Q, D>(prm, out_row0 + row, d4, acc);
     if (d4 == 0)
       store_final_lse<D>(prm, out_row0 + row, wsum > 0.f ? ms + fast_log2(wsum) * kLn2 : -INFINITY);
