@@ -112,7 +112,6 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long lon
 // Cost units charged per group by the balanced partition: starting and finishing a group
 // costs about 1.5 us, i.e. two 32 KB tiles of streaming or one 64 KB tile.
 static int group_overhead_for(int head_dim, int kv_dtype) {
-  if (const char* e = getenv("GQA_GROUP_OVERHEAD")) return atoi(e);
   return (kv_dtype == GQA_DTYPE_E4M3 || head_dim == 256) ? 1 : 2;
 }
 
