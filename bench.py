@@ -96,7 +96,8 @@ def kv_sets(name: str, world: int, batch: int = 16) -> int:
     return 1 if b >= 4 * L2_BYTES else int(math.ceil(4 * L2_BYTES / b))
 
 
-def static_config(name: str, world: int, batch: int = 16, page_size: int = 64, gather: str = "none") -> dict:
+def static_config(name: str, world: int, batch: int = 16, page_size: int = 64, gather: str = "none",
+                  page_order: str = "shuffled") -> dict:
     """The description both arms print as `config`: the workload, its shape, how it is split
     and how the timing keeps L2 out of the picture."""
     lens, hq, hkv, fp8 = shape_of(name, batch)
@@ -122,7 +123,7 @@ def static_config(name: str, world: int, batch: int = 16, page_size: int = 64, g
     else:
         cfg["parallelism"] = f"replica x{world}"
     if name == "paged":
-        cfg["kv_layout"] = f"paged_hnd, {page_size} rows per page, shuffled"
+        cfg["kv_layout"] = f"paged_hnd, {page_size} rows per page, {page_order}"
     elif name == "ragged":
         cfg["kv_layout"] = "packed"
     n = kv_sets(name, world, batch)
@@ -191,13 +192,14 @@ class Workload:
     """Device-resident inputs of one rank, the bound steps, and the parity check."""
 
     def __init__(self, name, rank, world, dev, batch=16, exchange="fused", gather="none", page_size=64,
-                 dependent_launch=True):
+                 dependent_launch=True, page_order="shuffled"):
         import gqa_decode_b200 as G
 
         self.G, self.name, self.rank, self.world, self.dev = G, name, rank, world, dev
         self.batch, self.page_size, self.pdl = batch, page_size, dependent_launch
+        self.page_order = page_order
         lens, hq, hkv, self.fp8 = shape_of(name, batch)
-        self.desc = static_config(name, world, batch, page_size, gather)
+        self.desc = static_config(name, world, batch, page_size, gather, page_order)
         self.scaling = "strong" if name in ("headshard", "headshard_fp8", "seqshard") else "weak"
         self.launches_per_step = 1
         self.collective = None
@@ -303,6 +305,8 @@ class Workload:
             pages = sum(need)
             g = torch.Generator(device=dev).manual_seed(99)
             order = torch.randperm(pages, generator=g, device=dev).to(torch.int32)
+            if self.page_order == "sequential":  # every sequence's pages in order, one after the other
+                order = torch.arange(pages, device=dev, dtype=torch.int32)
             table = torch.zeros(B, max(need), dtype=torch.int32, device=dev)
             at = 0
             for i, n in enumerate(need):
@@ -610,7 +614,7 @@ def reference_line(args, base, world):
         "impl": "reference", "value": val, "ms_per_step": dt * 1e3, "us_per_step": dt * 1e6,
         "scaling": "strong" if args.workload in ("headshard", "headshard_fp8", "seqshard") else "weak",
         "dtype": "f32 (bf16 inputs)",
-        "config": static_config(args.workload, world, args.batch, args.page_size, args.gather),
+        "config": static_config(args.workload, world, args.batch, args.page_size, args.gather, args.page_order),
         "cpu_baseline": {"value": val, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": what},
         "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -762,6 +766,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="headshard", choices=WORKLOADS)
     ap.add_argument("--page-size", type=int, default=64, help="paged workload: rows per page")
+    ap.add_argument("--page-order", default="shuffled", choices=["shuffled", "sequential"],
+                    help="paged workload: pool pages in random order, or each sequence's pages in a row")
     ap.add_argument("--batch", type=int, default=16, help="ragged / paged workloads: sequences per rank")
     ap.add_argument("--preheat-s", type=float, default=0.05,
                     help="seconds of untimed steps after the warm-up so the SM clock leaves its idle "
@@ -816,7 +822,8 @@ def main():
 
     def build(name, **kw):
         return Workload(name, rank, world, dev, args.batch, kw.get("exchange", args.exchange),
-                        kw.get("gather", args.gather), args.page_size, bool(args.dependent_launch))
+                        kw.get("gather", args.gather), args.page_size, bool(args.dependent_launch),
+                        args.page_order)
 
     def job_bytes_of(wl):
         nb = torch.tensor([float(wl.bytes_per_step)], device=dev, dtype=torch.float64)

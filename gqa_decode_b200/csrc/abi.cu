@@ -86,11 +86,15 @@ static EncodeTiledFn encode_fn() {
 }
 
 // View K (or V) as a row-major matrix [total_rows, row_bytes] and describe boxes of
-// [tile_rows x 128 bytes] with the 128-byte swizzle.  Rows past total_rows read as zero.
+// [box_rows x 128 bytes] with the 128-byte swizzle.  Rows past total_rows read as zero.
 // `row_elems` is the distance between consecutive rows in elements (head_dim, or
 // Hkv * head_dim when the heads of a page row are interleaved).
+// With `box_pieces` > 1 (a head's row is that many 128-byte pieces wide and a box spans them
+// all) the view is 3-D instead, [pieces of the row][rows][128 bytes] - the piece index is the
+// outermost coordinate although its stride is the smallest - so that ONE box brings the whole
+// tile in, laid out in shared memory piece after piece exactly as separate 2-D boxes would be.
 static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long long row_elems,
-                       long long total_rows, int tile_rows) {
+                       long long total_rows, int box_rows, int box_pieces) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return GQA_ERR_DRIVER;
   const bool fp8 = kv_dtype == GQA_DTYPE_E4M3;
@@ -98,13 +102,25 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long lon
   CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                : (kv_dtype == GQA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)total_rows};
-  cuuint64_t strides[1] = {(cuuint64_t)row_elems * esz};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)tile_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (box_pieces <= 1) {
+    cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)total_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_elems * esz};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[3] = {(cuuint64_t)(128 / esz), (cuuint64_t)total_rows,
+                          (cuuint64_t)(row_elems * esz / 128)};
+    cuuint64_t strides[2] = {(cuuint64_t)row_elems * esz, 128};
+    cuuint32_t box[3] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows, (cuuint32_t)box_pieces};
+    cuuint32_t estr[3] = {1, 1, 1};
+    r = enc(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : GQA_ERR_DRIVER;
 }
 
@@ -272,9 +288,13 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const bool nhd = a->kv_layout == GQA_LAYOUT_PAGED_NHD;
   const long long row_elems = nhd ? (long long)a->num_kv_heads * D : D;
   const long long map_rows = nhd ? a->total_rows / a->num_kv_heads : a->total_rows;
-  int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows);
+  // 128-byte pieces of one head's row; a box spans all of them unless it is shorter than the
+  // tile (small pages: the pieces of a tile then lie a whole tile apart in shared memory)
+  const int row_pieces = D * (a->kv_dtype == GQA_DTYPE_E4M3 ? 1 : 2) / 128;
+  const int box_pieces = box_rows == tile ? row_pieces : 1;
+  int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
   if (r) return r;
-  r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows);
+  r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
   if (r) return r;
 
   char* ws = static_cast<char*>(a->workspace);

@@ -990,7 +990,9 @@ struct Producer {
   }
   // Wait for the stage of tile `it` to be free, publish its descriptor and start the
   // loads (or just signal when there is no data).  All lanes call it; lane 0 acts.
-  __device__ __forceinline__ void post(const TileDesc& d, long long row) {
+  // `piece` is the first 128-byte piece of the head's row (non-zero only for page rows with
+  // interleaved heads).
+  __device__ __forceinline__ void post(const TileDesc& d, long long row, int piece = 0) {
     if (dead) return;
     if (wait_grid) {
       griddep_wait();
@@ -1021,12 +1023,13 @@ struct Producer {
         mbar_expect_tx(fb, Tr::kStageBytes);  // release: the descriptor is visible to waiters
         const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes;
         const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
-#pragma unroll
-        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-          tma_load_2d(kdst + bx * Tr::kBoxBytes, tm_k, fb, bx * Tr::kBoxCols, (int)row, policy);
-#pragma unroll
-        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-          tma_load_2d(vdst + bx * Tr::kBoxBytes, tm_v, fb, bx * Tr::kBoxCols, (int)row, policy);
+        if constexpr (Tr::kBoxesPerTensor == 1) {
+          tma_load_2d(kdst, tm_k, fb, piece * Tr::kBoxCols, (int)row, policy);
+          tma_load_2d(vdst, tm_v, fb, piece * Tr::kBoxCols, (int)row, policy);
+        } else {  // one box per tensor: all 128-byte pieces of the rows, piece after piece
+          tma_load_3d(kdst, tm_k, fb, 0, (int)row, piece, policy);
+          tma_load_3d(vdst, tm_v, fb, 0, (int)row, piece, policy);
+        }
       } else {
         mbar_arrive(fb);
       }
@@ -1036,7 +1039,28 @@ struct Producer {
     step();
   }
 
-  // Paged layouts: the tile holds keys [key0, key0 + d.valid) of sequence d.b, head d.h.
+  // Paged layouts with pages of at least a tile: the tile starting at key `key0` of sequence
+  // d.b lies inside one page; returns its first row in the tensor-map view (then post() as for
+  // the other layouts).  The block table is read 32 entries at a time, one per lane.
+  __device__ __forceinline__ int resolve_row(const TileDesc& d, int key0) {
+    const int ps = prm->page_size, psh = prm->page_shift;
+    const int pidx = psh >= 0 ? key0 >> psh : key0 / ps;
+    if (d.b != pg_seq || pidx < pg_base || pidx >= pg_base + 32) {
+      pg_seq = d.b;
+      pg_base = pidx;
+      const int e = pg_base + lane;
+      pg_entry = e < prm->table_stride
+                     ? __ldg(prm->block_table + (long long)d.b * prm->table_stride + e)
+                     : 0;
+    }
+    const int page = __shfl_sync(0xffffffffu, pg_entry, pidx - pg_base);
+    const int off = key0 - pidx * ps;
+    return prm->sched.layout == kLayoutPagedHnd ? (page * prm->sched.num_kv_heads + d.h) * ps + off
+                                                : page * ps + off;
+  }
+
+  // Paged layouts with pages shorter than a tile: the tile holds keys [key0, key0 + d.valid)
+  // of sequence d.b, head d.h.
   // It is fetched as boxes of prm->box_rows rows, each inside one page; lane j resolves and
   // issues box j, and boxes that start past the last valid key are not fetched (consumers
   // mask those rows).  The block table is read 32 entries at a time, one per lane.
@@ -1065,7 +1089,13 @@ struct Producer {
     const int pidx = psh >= 0 ? key >> psh : key / ps;
     const int page = __shfl_sync(0xffffffffu, pg_entry, min(pidx - pg_base, 31));
     int ok = 1;
+#ifdef GQA_PROFILE_WAITS
+    const long long w0 = clock64();
+#endif
     if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, prm->wait_limit_ns) ? 1 : 0;
+#ifdef GQA_PROFILE_WAITS
+    wait_cycles += clock64() - w0;
+#endif
     if (!__shfl_sync(0xffffffffu, ok, 0)) {
       if (lane == 0) atomicOr(prm->status, kStatusWaitEmpty);
       dead = true;
@@ -1288,7 +1318,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     pr.pg_seq = -1;
     pr.pg_base = 0;
     pr.pg_entry = 0;
-    const bool paged = prm.sched.layout >= kLayoutPagedHnd;
+    // 0: rows addressed directly; 1: pages of at least a tile (one box per tile and tensor);
+    // 2: smaller pages (several boxes per tile)
+    const int paged = prm.sched.layout < kLayoutPagedHnd ? 0 : (prm.box_rows == TILE ? 1 : 2);
+    const int nhd_pieces = prm.sched.layout == kLayoutPagedHnd ? 0 : Tr::kBoxesPerTensor;
     const int cta = blockIdx.x;
     TileDesc d;
     if (prm.sched.num_splits > 0) {
@@ -1316,7 +1349,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           d.valid = min(TILE, rows - t * TILE);
           d.flags = (t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0) |
                     (sg.first_slot < u0 ? kTileShared : 0);
-          if (paged) pr.post_paged(d, sg.row_begin + t * TILE);
+          if (paged == 2) pr.post_paged(d, sg.row_begin + t * TILE);
+          else if (paged) pr.post(d, pr.resolve_row(d, sg.row_begin + t * TILE), d.h * nhd_pieces);
           else pr.post(d, sg.kv_row0 + sg.row_begin + (long long)t * TILE);
         }
       }
@@ -1368,7 +1402,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const bool last = (wk.ti == wk.ntg - 1) || (t == t_end - 1 && !contiguous);
           d.valid = min(TILE, wk.len - wk.ti * TILE);
           d.flags = (open ? 0 : kTileFirst) | (last ? kTileLast : 0) | kTileShared;
-          if (paged) pr.post_paged(d, wk.ti * TILE);
+          if (paged == 2) pr.post_paged(d, wk.ti * TILE);
+          else if (paged) pr.post(d, pr.resolve_row(d, wk.ti * TILE), d.h * nhd_pieces);
           else pr.post(d, row0 + (long long)wk.ti * TILE);
           open = !last;
           wk.advance();
