@@ -51,9 +51,10 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 # DRAM bytes moved per algorithmic byte of the decode kernel, from ncu captures
-# (dram__bytes_read.sum + dram__bytes_write.sum over K+V bytes): bf16 ragged batch 1.017,
-# E4M3 batch 1.007
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": 1.017, "e4m3": 1.007}
+# (dram__bytes_read.sum + dram__bytes_write.sum over K+V bytes) on 537 MB launches, where the
+# traffic is in proportion to the keys streamed: bf16 (one sequence of 131072 keys) 1.011,
+# E4M3 (eight sequences of 32768 keys) 1.008
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bf16": 1.011, "e4m3": 1.008}
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126e6
 WORKLOADS = ["headshard", "headshard_fp8", "single", "ragged", "fp8", "paged", "seqshard"]
