@@ -289,9 +289,12 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const long long row_elems = nhd ? (long long)a->num_kv_heads * D : D;
   const long long map_rows = nhd ? a->total_rows / a->num_kv_heads : a->total_rows;
   // 128-byte pieces of one head's row; a box spans all of them unless it is shorter than the
-  // tile (small pages: the pieces of a tile then lie a whole tile apart in shared memory)
+  // tile (small pages: the pieces of a tile then lie a whole tile apart in shared memory).
   const int row_pieces = D * (a->kv_dtype == GQA_DTYPE_E4M3 ? 1 : 2) / 128;
-  const int box_pieces = box_rows == tile ? row_pieces : 1;
+  // (bf16/fp16 D=128 has instantiations for 16- and 32-row pages whose stage layout takes one
+  // box per page with all its pieces)
+  const bool page_boxes = !fp8 && D == 128 && (box_rows == 16 || box_rows == 32);
+  const int box_pieces = (box_rows == tile || page_boxes) ? row_pieces : 1;
   int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
   if (r) return r;
   r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
@@ -399,6 +402,22 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
     }
     if (upper) GQA_LAUNCH(Kv16Traits<__half, 256, 64, true>);
     GQA_LAUNCH(Kv16Traits<__half, 256, 64, false>);
+  }
+  if (D == 128 && page_boxes) {
+    if (box_rows == 16) {
+      if (bf) {
+        if (upper) GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, true, 4, 16>);
+        GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, false, 4, 16>);
+      }
+      if (upper) GQA_LAUNCH(Kv16Traits<__half, 128, 64, true, 4, 16>);
+      GQA_LAUNCH(Kv16Traits<__half, 128, 64, false, 4, 16>);
+    }
+    if (bf) {
+      if (upper) GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, true, 4, 32>);
+      GQA_LAUNCH(Kv16Traits<__nv_bfloat16, 128, 64, false, 4, 32>);
+    }
+    if (upper) GQA_LAUNCH(Kv16Traits<__half, 128, 64, true, 4, 32>);
+    GQA_LAUNCH(Kv16Traits<__half, 128, 64, false, 4, 32>);
   }
   if (D == 128) {
     if (bf) {

@@ -223,13 +223,24 @@ __device__ __forceinline__ void softmax_block(float (&s)[2 * NB][4], WarpState<D
 // D/64 separate boxes of [TILE x 128 B], each with the hardware 128-byte swizzle
 // (16-byte chunk index XOR (row & 7)), which makes every ldmatrix phase hit eight
 // different bank groups.
+// With BOXROWS < TILE (paged caches whose pages are shorter than a tile) a tile arrives as
+// TILE / BOXROWS boxes of [D/64 pieces x BOXROWS rows x 128 B] instead, one after the other:
+// a row's pieces then lie BOXROWS * 128 bytes apart and the 16-key blocks of different pages
+// a whole box apart (BOXROWS is a multiple of 16, so a block never straddles two boxes).
 // ---------------------------------------------------------------------------
-template <typename T16, int D, int TILE, bool UPPER, bool PARTIAL>
+template <int D, int TILE, int BOXROWS>
+__device__ __forceinline__ uint32_t tile_row_offset(int key) {
+  if constexpr (BOXROWS == TILE) return (uint32_t)key * 128u;
+  else return ((uint32_t)key / BOXROWS) * (uint32_t)((D / 64) * BOXROWS * 128) +
+              ((uint32_t)key % BOXROWS) * 128u;
+}
+
+template <typename T16, int D, int TILE, bool UPPER, bool PARTIAL, int BOXROWS = TILE>
 __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_base, int key0,
                                                  int valid, const uint32_t (&qa)[D / 16][4],
                                                  WarpState<D, UPPER>& st, float scale_log2,
                                                  int lane) {
-  constexpr uint32_t kBoxBytes = TILE * 128;
+  constexpr uint32_t kBoxBytes = BOXROWS * 128;
   float s[2][4];
 #pragma unroll
   for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -240,7 +251,7 @@ __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_bas
     for (int j = 0; j < 2; ++j) {
       const int key = key0 + 8 * j + (lane & 7);
       const int chunk = 2 * ks + (lane >> 3);
-      const uint32_t addr = k_base + (chunk >> 3) * kBoxBytes + key * 128 +
+      const uint32_t addr = k_base + (chunk >> 3) * kBoxBytes + tile_row_offset<D, TILE, BOXROWS>(key) +
                             (((chunk & 7) ^ (key & 7)) << 4);
       uint32_t r[4];
       ldsm_x4(r, addr);
@@ -258,8 +269,8 @@ __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_bas
   for (int nt = 0; nt < D / 8; nt += 2) {
     const int key = key0 + ((lane >> 3) & 1) * 8 + (lane & 7);
     const int chunk = nt + (lane >> 4);
-    const uint32_t addr =
-        v_base + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+    const uint32_t addr = v_base + (chunk >> 3) * kBoxBytes + tile_row_offset<D, TILE, BOXROWS>(key) +
+                          (((chunk & 7) ^ (key & 7)) << 4);
     uint32_t r[4];
     ldsm_x4_trans(r, addr);
     if (PARTIAL) {
@@ -277,8 +288,9 @@ __device__ __forceinline__ void consume_block_16(uint32_t k_base, uint32_t v_bas
   }
 }
 
-template <typename T16_, int D_, int TILE_, bool UPPER_, int WARPS_ = 4>
+template <typename T16_, int D_, int TILE_, bool UPPER_, int WARPS_ = 4, int BOXROWS_ = TILE_>
 struct Kv16Traits {
+  static constexpr int kBoxRows = BOXROWS_;  // rows per TMA box: the tile, or a shorter page
   using Q = T16_;
   static constexpr int D = D_;
   static constexpr int TILE = TILE_;
@@ -307,8 +319,8 @@ struct Kv16Traits {
 #pragma unroll
     for (int b = 0; b < NB; ++b)
       if (!PARTIAL || key0 + 16 * b < valid)
-        consume_block_16<Q, D, TILE, UPPER, PARTIAL>(k_base, v_base, key0 + 16 * b, valid, qa, st,
-                                                     scale_log2, lane);
+        consume_block_16<Q, D, TILE, UPPER, PARTIAL, kBoxRows>(k_base, v_base, key0 + 16 * b, valid,
+                                                               qa, st, scale_log2, lane);
   }
   // Load the A fragments of Q for k-step ks: thread holds d = 16*ks + 2c + {0,1} and +8.
   __device__ static __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const Q* row0,
@@ -1114,14 +1126,25 @@ struct Producer {
       const bool hnd = prm->sched.layout == kLayoutPagedHnd;
       const int row = hnd ? (page * prm->sched.num_kv_heads + d.h) * ps + off : page * ps + off;
       const int col0 = hnd ? 0 : d.h * (Tr::kBoxCols * Tr::kBoxesPerTensor);
-      const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes + ((uint32_t)lane << (bsh + 7));
-      const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+      if constexpr (Tr::kBoxRows < Tr::TILE) {
+        // instantiation for one page size: a box brings all 128-byte pieces of the page's rows
+        // (3-D view) and the boxes of a tile follow each other in the stage
+        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes +
+                              (uint32_t)lane * (Tr::kBoxesPerTensor * Tr::kBoxRows * 128);
+        const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
+        const int piece0 = hnd ? 0 : d.h * Tr::kBoxesPerTensor;
+        tma_load_3d(kdst, tm_k, fb, 0, row, piece0, policy);
+        tma_load_3d(vdst, tm_v, fb, 0, row, piece0, policy);
+      } else {
+        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes + ((uint32_t)lane << (bsh + 7));
+        const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
 #pragma unroll
-      for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-        tma_load_2d(kdst + bx * Tr::kBoxBytes, tm_k, fb, col0 + bx * Tr::kBoxCols, row, policy);
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(kdst + bx * Tr::kBoxBytes, tm_k, fb, col0 + bx * Tr::kBoxCols, row, policy);
 #pragma unroll
-      for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
-        tma_load_2d(vdst + bx * Tr::kBoxBytes, tm_v, fb, col0 + bx * Tr::kBoxCols, row, policy);
+        for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)
+          tma_load_2d(vdst + bx * Tr::kBoxBytes, tm_v, fb, col0 + bx * Tr::kBoxCols, row, policy);
+      }
     }
     __syncwarp();
     step();

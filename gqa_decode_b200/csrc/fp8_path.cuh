@@ -223,6 +223,7 @@ struct KvFp8Traits {
   static constexpr int kMergeBatch = 8;      // partials merged per L2 round trip
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
+  static constexpr int kBoxRows = TILE_;  // small pages keep per-page 2-D boxes (rows are one piece)
   static constexpr int kBoxBytes = TILE * 128;
   static constexpr int kStageBytes = 2 * kBoxBytes;
   static constexpr int kBoxCols = 128;
