@@ -24,6 +24,7 @@ amax_kernel(const T16* __restrict__ x, long long elems_per_group, float* __restr
   const uint4* p = reinterpret_cast<const uint4*>(x + g * elems_per_group);
   const long long n8 = elems_per_group / 8;
   float m = 0.f;
+#pragma unroll 4
   for (long long i = (long long)blockIdx.x * kQuantThreads + threadIdx.x; i < n8;
        i += (long long)gridDim.x * kQuantThreads) {
     const uint4 v = __ldg(p + i);
@@ -45,35 +46,62 @@ amax_kernel(const T16* __restrict__ x, long long elems_per_group, float* __restr
   }
 }
 
+// x / a, correctly rounded, for many x and one divisor a whose correctly rounded reciprocal is
+// r: the quotient estimate x * r corrected once with the exact remainder (two fused
+// multiply-adds instead of the dozen instructions of a general division).  Exact whenever
+// the significand of a is not all ones and r is a normal number - a is a 16-bit float's
+// value here (8 or 11 significant bits; checked against the division for every pair of
+// significands), and divisors beyond 2^100, whose reciprocals are subnormal, take the general
+// division.
+__device__ __forceinline__ float divide_by(float x, float a, float r) {
+  if (a > 0x1p100f) return __fdiv_rn(x, a);
+  const float q = __fmul_rn(x, r);
+  return __fmaf_rn(__fmaf_rn(-a, q, x), r, q);
+}
+
+// Eight 16-bit values -> eight E4M3 codes: float(x) / amax * 448, clamped to the E4M3 range,
+// rounded to nearest even.
+template <typename T16>
+__device__ __forceinline__ uint2 quantize8(const uint4 v, float a, float r) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const T16 lo = *reinterpret_cast<const T16*>(&w[j]);
+    const T16 hi = *(reinterpret_cast<const T16*>(&w[j]) + 1);
+    float f0 = __fmul_rn(divide_by(Mma16<T16>::to_float(lo), a, r), 448.f);
+    float f1 = __fmul_rn(divide_by(Mma16<T16>::to_float(hi), a, r), 448.f);
+    f0 = fminf(fmaxf(f0, -448.f), 448.f);
+    f1 = fminf(fmaxf(f1, -448.f), 448.f);
+    const unsigned short pr = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
+    out[j >> 1] |= (uint32_t)pr << (16 * (j & 1));
+  }
+  return make_uint2(out[0], out[1]);
+}
+
 template <typename T16>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_kernel(const T16* __restrict__ x, long long elems_per_group, const float* __restrict__ amax,
                 uint8_t* __restrict__ codes, float* __restrict__ scale) {
   const long long g = blockIdx.y;
   const float a = fmaxf(amax[g], 1e-12f);
+  const float r = __frcp_rn(a);
   if (blockIdx.x == 0 && threadIdx.x == 0) scale[g] = __fdiv_rn(a, 448.f);
   const uint4* p = reinterpret_cast<const uint4*>(x + g * elems_per_group);
   uint2* q = reinterpret_cast<uint2*>(codes + g * elems_per_group);
   const long long n8 = elems_per_group / 8;
-  for (long long i = (long long)blockIdx.x * kQuantThreads + threadIdx.x; i < n8;
-       i += (long long)gridDim.x * kQuantThreads) {
-    const uint4 v = __ldg(p + i);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t out[2] = {0u, 0u};
+  const long long stride = (long long)gridDim.x * kQuantThreads;
+  long long i = (long long)blockIdx.x * kQuantThreads + threadIdx.x;
+  // four 16-byte loads in flight per thread before the first conversion
+  constexpr int kAhead = 4;
+  for (; i + (kAhead - 1) * stride < n8; i += kAhead * stride) {
+    uint4 v[kAhead];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const T16 lo = *reinterpret_cast<const T16*>(&w[j]);
-      const T16 hi = *(reinterpret_cast<const T16*>(&w[j]) + 1);
-      // float(x) / amax * 448, clamped to the E4M3 range, rounded to nearest even
-      float f0 = __fmul_rn(__fdiv_rn(Mma16<T16>::to_float(lo), a), 448.f);
-      float f1 = __fmul_rn(__fdiv_rn(Mma16<T16>::to_float(hi), a), 448.f);
-      f0 = fminf(fmaxf(f0, -448.f), 448.f);
-      f1 = fminf(fmaxf(f1, -448.f), 448.f);
-      const unsigned short pr = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
-      out[j >> 1] |= (uint32_t)pr << (16 * (j & 1));
-    }
-    q[i] = make_uint2(out[0], out[1]);
+    for (int u = 0; u < kAhead; ++u) v[u] = __ldg(p + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) q[i + u * stride] = quantize8<T16>(v[u], a, r);
   }
+  for (; i < n8; i += stride) q[i] = quantize8<T16>(__ldg(p + i), a, r);
 }
 
 // Append one token per sequence to E4M3 caches whose per-(sequence, head) scales are

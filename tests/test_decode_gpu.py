@@ -389,3 +389,35 @@ def test_gpu_quantise_is_bit_identical_to_reference_arithmetic(G):
                                                from_bits(z["v"], torch.bfloat16).to(DEV))
     assert np.array_equal(k8.cpu().view(torch.uint8).numpy(), z["k8"])
     assert np.array_equal(ks.cpu().numpy(), z["k_scale"]) and np.array_equal(vs.cpu().numpy(), z["v_scale"])
+
+
+def test_gpu_quantise_division_every_significand_pair(G):
+    """The quantise kernel divides by a head's amax with a reciprocal and one exact-remainder
+    correction.  One head per amax significand (128 of them in bf16), each holding every bf16
+    magnitude up to its amax over a range of exponents, both signs: codes must equal the
+    oracle's (true division) bit for bit.  Further heads with amax near the top and the bottom
+    of the bf16 range take the general division path and the clamp."""
+    from gqa_decode_b200 import fp8_utils
+
+    heads = []
+    exps = torch.arange(-12, 1, dtype=torch.float32)              # x spans 13 binades below amax
+    mant = 1.0 + torch.arange(128, dtype=torch.float32) / 128.0   # all bf16 significands
+    grid = (mant[None, :] * torch.exp2(exps)[:, None]).reshape(-1)  # 13 * 128 magnitudes in (2^-12, 2)
+    for ma in range(128):
+        a = 1.0 + ma / 128.0
+        x = grid[grid <= a]
+        x = torch.cat([x, -x, torch.tensor([a, 0.0])])
+        pad = 2 * grid.numel() + 2 - x.numel()
+        heads.append(torch.cat([x, torch.zeros(pad)]))
+    base = torch.stack(heads)                                     # [128, 3330]
+    n = base.shape[1]
+    n8 = (n + 127) // 128 * 128
+    base = torch.nn.functional.pad(base, (0, n8 - n))
+    for scale in (1.0, 2.0 ** 120, 2.0 ** -120, 3.0e-13):
+        k = (base * scale).to(torch.bfloat16).view(128, n8 // 128, 128)
+        v = k.flip(0).contiguous()
+        k8, v8, ks, vs = fp8_utils.quantize_kv_fp8(k.to(DEV), v.to(DEV))
+        r8k, r8v, rks, rvs = O.quantize_kv_e4m3(k, v)
+        assert torch.equal(k8.cpu().view(torch.uint8), r8k.view(torch.uint8)), scale
+        assert torch.equal(v8.cpu().view(torch.uint8), r8v.view(torch.uint8)), scale
+        assert torch.equal(ks.cpu(), rks) and torch.equal(vs.cpu(), rvs)
