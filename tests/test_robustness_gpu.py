@@ -204,3 +204,55 @@ def test_one_caller_workspace_many_geometries(G):
         out = G.gqa_decode_attention_batched(q, k, v, None, workspace=junk)
         assert G.read_status(junk) == 0
         assert within_tolerance(out.cpu(), ref)[0]
+
+
+@pytest.mark.parametrize("mode", ["balanced", "splits", "stealing", "ticket", "separate", "fp8"])
+def test_workspace_guards_stay_intact(G, mode):
+    """A workspace of exactly the advertised size between two guard areas: a launch may write
+    nothing outside [workspace, workspace + workspace_bytes), leaves the guards' pattern alone
+    and hands the workspace itself back all zero (what the next launch relies on)."""
+    from gqa_decode_b200 import fp8_utils
+
+    b, hq, hkv, d = 5, 32, 8, 128
+    lens = [1, 4097, 0, 9000, 650]
+    gen = torch.Generator().manual_seed(23)
+    q = O.randn_bf16((b, hq, d), gen)
+    ks = [O.randn_bf16((hkv, l, d), gen) for l in lens]
+    vs = [O.randn_bf16((hkv, l, d), gen) for l in lens]
+    smax = 9000
+    k = torch.zeros(b, hkv, smax, d, dtype=torch.bfloat16)
+    v = torch.zeros_like(k)
+    for i, l in enumerate(lens):
+        k[i, :, :l], v[i, :, :l] = ks[i], vs[i]
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    splits = 5 if mode == "splits" else 0
+    need = G.workspace_bytes(b, hq, hkv, d, splits)
+    guard = 1 << 16
+    buf = torch.full((guard + need + guard,), 0xAB, dtype=torch.uint8, device=DEV)
+    ws = buf[guard:guard + need]
+    assert ws.data_ptr() % 256 == 0
+    ws.zero_()
+    kw = dict(workspace=ws, num_splits=splits or None)
+    if mode == "stealing":
+        kw["work_stealing"] = True
+    if mode == "ticket":
+        kw["ticket_merge"] = True
+    if mode == "separate":
+        kw["separate_merge"] = True
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    if mode == "fp8":
+        k8, v8, kscale, vscale = fp8_utils.quantize_kv_fp8(kd.view(b * hkv, smax, d), vd.view(b * hkv, smax, d))
+        kd, vd = k8.view(b, hkv, smax, d), v8.view(b, hkv, smax, d)
+        kw.update(k_scale=kscale.view(b, hkv), v_scale=vscale.view(b, hkv))
+    for _ in range(3):
+        out = G.gqa_decode_attention_batched(qd, kd, vd, sl, **kw)
+    assert G.read_status(ws) == 0
+    assert bool((buf[:guard] == 0xAB).all()) and bool((buf[guard + need:] == 0xAB).all())
+    if mode in ("balanced", "splits", "fp8"):
+        # the default merge hands every partial back as zeros (the ticket-based modes only
+        # promise zero control words and leave old partials behind)
+        assert int(ws.count_nonzero().item()) == 0
+    if mode != "fp8":
+        ref = O.attend_batch(q, ks, vs)
+        ok, ratio, mx = within_tolerance(out.cpu(), ref)
+        assert ok, (mode, ratio, mx)
