@@ -116,6 +116,42 @@ SIGNATURES = {
 _lib = None
 
 
+class _NoRange:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _NvtxRange:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        import torch
+
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+_NO_RANGE = _NoRange()
+TRACE_RANGES = os.environ.get("GQA_DECODE_B200_NVTX", "0") == "1"
+
+
+def trace_range(name: str):
+    """``with trace_range("gqa_decode:launch"): ...`` - an NVTX range around a host-side phase
+    (launch of the decode kernel, the exchange, the collective + merge) when the environment
+    variable GQA_DECODE_B200_NVTX=1 was set at import; a shared no-op object otherwise.  The
+    pre-bound ``DecodePlan.run`` carries none: it is one C call."""
+    return _NvtxRange(name) if TRACE_RANGES else _NO_RANGE
+
+
 def lib_path() -> str:
     """Path of the shared library: the in-tree build, or the file named by the environment
     variable GQA_DECODE_B200_LIB (a differently configured build of the same sources)."""

@@ -17,6 +17,8 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from ._native import trace_range as _trace_range
+
 
 def next_epoch(epoch: int) -> int:
     """Epoch of the step after `epoch`.  Epochs are 32-bit, never 0 (0 means "no step yet" in
@@ -113,13 +115,14 @@ class NvlinkExchange:
         _refuse_capture("NvlinkExchange.merge")
         self.epoch = next_epoch(self.epoch)
         code = {torch.bfloat16: n.DTYPE_BF16, torch.float16: n.DTYPE_FP16}.get(out.dtype, 0)
-        n.check(
-            self._lib.gqa_exchange_merge(
-                o32.data_ptr(), lse.data_ptr(), self.handle.buffer_ptrs_dev, self.rank, self.world,
-                self.epoch, self.rows, self.head_dim, None if f32 else out.data_ptr(), code,
-                out.data_ptr() if f32 else None, None, self.status.data_ptr(), self.wait_limit_ns,
-                torch.cuda.current_stream(self.device).cuda_stream),
-            "gqa_exchange_merge")
+        with n.trace_range("gqa_decode:exchange_merge"):
+            n.check(
+                self._lib.gqa_exchange_merge(
+                    o32.data_ptr(), lse.data_ptr(), self.handle.buffer_ptrs_dev, self.rank, self.world,
+                    self.epoch, self.rows, self.head_dim, None if f32 else out.data_ptr(), code,
+                    out.data_ptr() if f32 else None, None, self.status.data_ptr(), self.wait_limit_ns,
+                    torch.cuda.current_stream(self.device).cuda_stream),
+                "gqa_exchange_merge")
         return out
 
     def check(self) -> int:
@@ -332,7 +335,8 @@ def sequence_sharded_decode(
     the CUDA kernels.
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    o32, lse = local_fn(q, k_shard, v_shard, seq_lens_shard, **kw)
+    with _trace_range("gqa_decode:local_partial"):
+        o32, lse = local_fn(q, k_shard, v_shard, seq_lens_shard, **kw)
     b, hq, d = o32.shape
     if exchange is not None:
         return exchange.merge(o32.reshape(b * hq, d), lse.reshape(b * hq), q.dtype).view(b, hq, d)
@@ -341,9 +345,11 @@ def sequence_sharded_decode(
     # one message per rank: [B*Hq, D+1] = normalised output with its log-sum-exp appended
     mine = torch.cat([o32.reshape(b * hq, d), lse.reshape(b * hq, 1)], dim=1).contiguous()
     flat = torch.empty((world * b * hq, d + 1), dtype=mine.dtype, device=mine.device)
-    dist.all_gather_into_tensor(flat, mine, group=group)  # rank-major concatenation
+    with _trace_range("gqa_decode:all_gather"):
+        dist.all_gather_into_tensor(flat, mine, group=group)  # rank-major concatenation
     gathered = flat.view(world, b * hq, d + 1)
-    out = merge_fn(gathered[:, :, :d].contiguous(), gathered[:, :, d].contiguous(), q.dtype)
+    with _trace_range("gqa_decode:merge_partials"):
+        out = merge_fn(gathered[:, :, :d].contiguous(), gathered[:, :, d].contiguous(), q.dtype)
     return out.view(b, hq, d)
 
 

@@ -452,7 +452,7 @@ def gqa_decode_attention_batched(
         plan = DecodePlan(fn, a, dev, result, keep, ws)
         plan._geometry = geometry
         return plan
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _native.trace_range("gqa_decode:launch"):
         _native.check(fn(ctypes.byref(a)), "gqa_decode_attention")
     return result
 

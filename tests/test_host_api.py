@@ -121,3 +121,32 @@ def test_epochs_wrap_without_zero_and_keep_alternating():
     assert all(x != 0 and x <= 0xFFFFFFFF for x in seen)
     assert all((x & 1) != (y & 1) for x, y in zip(seen, seen[1:]))  # the buffer halves keep alternating
     assert next_epoch(0) == 1
+
+
+def test_optional_nvtx_ranges(monkeypatch):
+    """With GQA_DECODE_B200_NVTX=1 the host-side phases are wrapped in NVTX ranges (pushed and
+    popped in pairs, in order); without it trace_range() hands out one shared no-op object."""
+    import torch
+
+    from gqa_decode_b200 import _native, distributed
+
+    assert _native.trace_range("a") is _native.trace_range("b")  # disabled: the shared no-op
+    seen = []
+    monkeypatch.setattr(_native, "TRACE_RANGES", True)
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: seen.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: seen.append(("pop",)))
+
+    def local_fn(q, k, v, lens, **kw):
+        b, hq, d = q.shape
+        return torch.zeros(b, hq, d), torch.zeros(b, hq)
+
+    def merge_fn(o, lse, dtype):
+        return o[0].to(dtype)
+
+    q = torch.zeros(2, 4, 8, dtype=torch.bfloat16)
+    out = distributed.sequence_sharded_decode(q, None, None, None, local_fn=local_fn, merge_fn=merge_fn)
+    assert out.shape == (2, 4, 8)
+    assert seen == [("push", "gqa_decode:local_partial"), ("pop",)]
+    with _native.trace_range("x"):
+        pass
+    assert seen[-2:] == [("push", "x"), ("pop",)]
