@@ -93,8 +93,9 @@ static EncodeTiledFn encode_fn() {
 // all) the view is 3-D instead, [pieces of the row][rows][128 bytes] - the piece index is the
 // outermost coordinate although its stride is the smallest - so that ONE box brings the whole
 // tile in, laid out in shared memory piece after piece exactly as separate 2-D boxes would be.
+// Heads narrower than 128 bytes (E4M3 with head_dim 64) get boxes of their own width, unswizzled.
 static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long long row_elems,
-                       long long total_rows, int box_rows, int box_pieces) {
+                       long long total_rows, int box_rows, int box_pieces, int head_dim) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return GQA_ERR_DRIVER;
   const bool fp8 = kv_dtype == GQA_DTYPE_E4M3;
@@ -106,10 +107,12 @@ static int make_kv_map(CUtensorMap* tm, const void* base, int kv_dtype, long lon
   if (box_pieces <= 1) {
     cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)total_rows};
     cuuint64_t strides[1] = {(cuuint64_t)row_elems * esz};
-    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
+    const bool narrow = head_dim * esz < 128;
+    cuuint32_t box[2] = {(cuuint32_t)(narrow ? head_dim : 128 / esz), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE,
+            narrow ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   } else {
     cuuint64_t dims[3] = {(cuuint64_t)(128 / esz), (cuuint64_t)total_rows,
@@ -136,7 +139,7 @@ static int group_overhead_for(int head_dim, int kv_dtype) {
 constexpr int kFp8Warps = 8;
 constexpr int kFp8Tile = 256;
 static int tile_rows_for(int head_dim, int kv_dtype) {
-  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? kFp8Tile : 0;
+  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? kFp8Tile : head_dim == 64 ? 128 : 0;
   if (head_dim == 256) return 64;
   if (head_dim == 128) return 64;
   if (head_dim == 64) return 128;
@@ -295,9 +298,9 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   // box per page with all its pieces)
   const bool page_boxes = !fp8 && D == 128 && (box_rows == 16 || box_rows == 32);
   const int box_pieces = (box_rows == tile || page_boxes) ? row_pieces : 1;
-  int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
+  int r = make_kv_map(&tk, a->k, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces, D);
   if (r) return r;
-  r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces);
+  r = make_kv_map(&tv, a->v, a->kv_dtype, row_elems, map_rows, box_rows, box_pieces, D);
   if (r) return r;
 
   char* ws = static_cast<char*>(a->workspace);
@@ -378,6 +381,14 @@ static int run_decode(const gqa_decode_args_t* a, bool want_fp8, bool force_bala
   const bool bf = a->q_dtype == GQA_DTYPE_BF16;
 #define GQA_LAUNCH(...) \
   return launch_decode<__VA_ARGS__>(tk, tv, prm, num_ctas, st, separate, groups)
+  if (fp8 && D == 64) {  // every element rounded like dequantize_kv_fp8, K and V alike
+    if (bf) {
+      if (upper) GQA_LAUNCH(KvFp8Dim64Traits<__nv_bfloat16, true>);
+      GQA_LAUNCH(KvFp8Dim64Traits<__nv_bfloat16, false>);
+    }
+    if (upper) GQA_LAUNCH(KvFp8Dim64Traits<__half, true>);
+    GQA_LAUNCH(KvFp8Dim64Traits<__half, false>);
+  }
   if (fp8) {
     const bool exact_v = (a->flags & GQA_FLAG_FP8_EXACT_V) != 0;
     if (exact_v) {

@@ -301,6 +301,8 @@ struct Kv16Traits {
   static constexpr int kBoxesPerTensor = D * 2 / 128;          // TMA boxes per K (or V) tile
   static constexpr int kBoxBytes = TILE * 128;
   static constexpr int kStageBytes = 2 * kBoxesPerTensor * kBoxBytes;
+  static constexpr int kTxBytes = kStageBytes;                 // bytes the loads of a full tile bring
+  static constexpr int kPieceBytes = 128;                      // bytes of one box row
   static constexpr int kBoxCols = 64;                          // elements per box row
   static constexpr int kMoStride = D + 8;  // floats per merge row; +8 keeps float2 stores conflict-free
   // float index of (merge row, column) inside a warp's block of merge rows
@@ -1032,7 +1034,7 @@ struct Producer {
       *sm_published = (int)(it + 1);
       const uint32_t fb = full0 + 8 * s;
       if (d.valid > 0) {
-        mbar_expect_tx(fb, Tr::kStageBytes);  // release: the descriptor is visible to waiters
+        mbar_expect_tx(fb, Tr::kTxBytes);  // release: the descriptor is visible to waiters
         const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes;
         const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
         if constexpr (Tr::kBoxesPerTensor == 1) {
@@ -1118,7 +1120,7 @@ struct Producer {
       sm_desc[it % kDescRing] = d;
       __threadfence_block();
       *sm_published = (int)(it + 1);
-      mbar_expect_tx(fb, ((uint32_t)nbox << bsh) * 128u * 2u * Tr::kBoxesPerTensor);
+      mbar_expect_tx(fb, ((uint32_t)nbox << bsh) * (uint32_t)Tr::kPieceBytes * 2u * Tr::kBoxesPerTensor);
     }
     __syncwarp();
     if (lane < nbox) {
@@ -1136,7 +1138,7 @@ struct Producer {
         tma_load_3d(kdst, tm_k, fb, 0, row, piece0, policy);
         tma_load_3d(vdst, tm_v, fb, 0, row, piece0, policy);
       } else {
-        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes + ((uint32_t)lane << (bsh + 7));
+        const uint32_t kdst = stage_addr0 + s * Tr::kStageBytes + ((uint32_t)lane << bsh) * Tr::kPieceBytes;
         const uint32_t vdst = kdst + Tr::kBoxesPerTensor * Tr::kBoxBytes;
 #pragma unroll
         for (int bx = 0; bx < Tr::kBoxesPerTensor; ++bx)

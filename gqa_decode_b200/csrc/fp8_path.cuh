@@ -226,6 +226,8 @@ struct KvFp8Traits {
   static constexpr int kBoxRows = TILE_;  // small pages keep per-page 2-D boxes (rows are one piece)
   static constexpr int kBoxBytes = TILE * 128;
   static constexpr int kStageBytes = 2 * kBoxBytes;
+  static constexpr int kTxBytes = kStageBytes;
+  static constexpr int kPieceBytes = 128;
   static constexpr int kBoxCols = 128;
   struct Extra {
     float ks, vs;
@@ -259,6 +261,89 @@ struct KvFp8Traits {
     }
   }
   // d index of accumulator element (n-tile nt, thread column c, element e).
+  __device__ static __forceinline__ int out_col(int nt, int c, int e) { return 8 * nt + 2 * c + e; }
+};
+
+// ---------------------------------------------------------------------------
+// E4M3 K/V with head_dim 64 (accepted by the reference's FP8 kernels,
+// gqa_decode/gqa_decode.py:1466-1467).  Rows are 64 bytes, so the permuted fragment loads
+// above do not apply; instead each consumer warp dequantises the 16 keys of a block exactly
+// like dequantize_kv_fp8 (gqa_decode/fp8_utils.py:54-55: float32(code) * scale, rounded to the
+// 16-bit type - K and V alike) into a scratch of its own behind the stage's raw bytes, laid out
+// as the 128-byte-swizzled rows the 16-bit consumer reads, and then runs that consumer on it.
+// Tiles of 128 keys: [128 x 64 B] for K and for V, unswizzled.
+// ---------------------------------------------------------------------------
+template <typename T16_, bool UPPER_>
+struct KvFp8Dim64Traits {
+  using Q = T16_;
+  static constexpr int D = 64;
+  static constexpr int TILE = 128;
+  static constexpr bool UPPER = UPPER_;
+  static constexpr int kWarps = 4;
+  static constexpr int kGroups = 1;
+  static constexpr bool kFp8 = true;
+  static constexpr int kBoxesPerTensor = 1;
+  static constexpr int kBoxRows = TILE;
+  static constexpr int kPieceBytes = 64;                 // bytes of one box row
+  static constexpr int kBoxBytes = TILE * kPieceBytes;   // raw K (or V) bytes of a tile
+  static constexpr int kTxBytes = 2 * kBoxBytes;
+  static constexpr int kScratchBytes = 2 * 16 * 128;     // per warp: 16 keys of K, 16 of V, 16-bit
+  static constexpr int kStageBytes = kTxBytes + kWarps * kScratchBytes;
+  static constexpr int kBoxCols = 64;
+  static constexpr int kMoStride = D + 8;
+  __device__ static __forceinline__ int mo_index(int row, int col) { return row * kMoStride + col; }
+  static constexpr int kMergeBatch = 8;
+  struct Extra {
+    float ks, vs;
+  };
+  __device__ static __forceinline__ void begin_segment(Extra& e, const DecodeParams& prm, int b,
+                                                       int h) {
+    const long long g = (long long)b * prm.sched.num_kv_heads + h;
+    e.ks = __ldg(prm.k_scale + g);
+    e.vs = __ldg(prm.v_scale + g);
+  }
+  __device__ static __forceinline__ float out_scale(const Extra&) { return 1.f; }
+  // 16 rows of 64 codes at `src` (rows 64 bytes apart) -> 16 rows of 64 16-bit values at
+  // `dst` (rows 128 bytes apart, 16-byte chunk c of row r at chunk position c ^ (r & 7)).
+  // Lane l converts the 32 bytes of half (l & 1) of row (l >> 1).
+  __device__ static __forceinline__ void dequant_rows(uint32_t src, uint32_t dst, float scale, int lane) {
+    const int r = lane >> 1, h = lane & 1;
+    const uint4 a = lds128(src + lane * 32), b = lds128(src + lane * 32 + 16);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t o[16];
+    dequant_words<Q, 8>(w, scale, o);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t at = dst + r * 128 + (((4 * h + c) ^ (r & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at), "r"(o[4 * c]), "r"(o[4 * c + 1]),
+                   "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                   : "memory");
+    }
+  }
+  template <bool PARTIAL, int NB>
+  __device__ static __forceinline__ void consume(uint32_t k_base, uint32_t v_base, int key0,
+                                                 int valid, const uint32_t (&qa)[D / 16][4],
+                                                 WarpState<D, UPPER>& st, float scale_log2,
+                                                 int lane, const Extra& e) {
+    // this warp's scratch sits behind the raw bytes of the stage; warp = key0 / (16 * NB)
+    const uint32_t scratch = k_base + kTxBytes + (uint32_t)(key0 / (16 * NB)) * kScratchBytes;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      const int k0 = key0 + 16 * b;
+      if (PARTIAL && k0 >= valid) break;
+      __syncwarp();  // the previous block's fragment loads are done with the scratch
+      dequant_rows(k_base + k0 * kPieceBytes, scratch, e.ks, lane);
+      dequant_rows(v_base + k0 * kPieceBytes, scratch + 16 * 128, e.vs, lane);
+      __syncwarp();
+      // the 16-bit consumer addresses rows as key * 128 from its base: rebase to the scratch
+      consume_block_16<Q, D, TILE, UPPER, PARTIAL>(scratch - k0 * 128, scratch + 16 * 128 - k0 * 128, k0,
+                                                   valid, qa, st, scale_log2, lane);
+    }
+  }
+  __device__ static __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const Q* row0,
+                                                const Q* row1, bool v0, bool v1, int c) {
+    Kv16Traits<Q, D, TILE, UPPER>::load_q(qa, row0, row1, v0, v1, c);
+  }
   __device__ static __forceinline__ int out_col(int nt, int c, int e) { return 8 * nt + 2 * c + e; }
 };
 

@@ -369,8 +369,8 @@ def gqa_decode_attention_batched(
         raise ValueError("num_q_heads must be divisible by num_kv_heads")
     if num_q_heads // num_kv_heads > 16:
         raise ValueError("group size must be in [1, 16]")
-    if head_dim not in ((128,) if fp8 else (64, 128, 256)):
-        raise ValueError("head_dim must be 64, 128 or 256 (128 for FP8)")
+    if head_dim not in ((64, 128) if fp8 else (64, 128, 256)):
+        raise ValueError("head_dim must be 64, 128 or 256 (64 or 128 for FP8)")
     if seq_lens is not None:
         if seq_lens.dtype != torch.int32 or seq_lens.device != q.device or seq_lens.numel() != batch:
             raise ValueError("seq_lens must be an int32 CUDA tensor of shape [batch]")

@@ -93,7 +93,7 @@ typedef struct gqa_decode_args {
   int32_t batch;
   int32_t num_q_heads;
   int32_t num_kv_heads;
-  int32_t head_dim;         /* 64, 128 or 256 (E4M3: 128) */
+  int32_t head_dim;         /* 64, 128 or 256 (E4M3: 64 or 128) */
   int32_t max_seq_len;      /* rows per head slab (padded layout); bound on every length */
   int64_t total_rows;       /* rows of the whole K (= V) allocation, viewed as [rows, head_dim]
                                (paged: num_pages * num_kv_heads * page_size) */

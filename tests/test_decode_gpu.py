@@ -421,3 +421,80 @@ def test_gpu_quantise_division_every_significand_pair(G):
         assert torch.equal(k8.cpu().view(torch.uint8), r8k.view(torch.uint8)), scale
         assert torch.equal(v8.cpu().view(torch.uint8), r8v.view(torch.uint8)), scale
         assert torch.equal(ks.cpu(), rks) and torch.equal(vs.cpu(), rvs)
+
+
+@pytest.mark.parametrize("hq,hkv,dtype", [(32, 8, torch.bfloat16), (16, 1, torch.bfloat16), (8, 8, torch.float16)])
+@pytest.mark.parametrize("s", [1, 127, 129, 4096, 20000])
+def test_fp8_head_dim_64(G, hq, hkv, dtype, s):
+    """E4M3 caches with head_dim 64 (accepted by the reference's FP8 kernels,
+    gqa_decode/gqa_decode.py:1466-1467): every K and V element is rounded like
+    dequantize_kv_fp8, so the result must sit inside the tolerance of the oracle's
+    quantise -> dequantise -> attend path, explicit splits and the python reduction included."""
+    g = torch.Generator().manual_seed(77 + s)
+    q = O.randn_bf16((hq, 64), g).to(dtype)
+    k, v = O.outlier_kv((hkv, s, 64), g, rate=1e-3).to(dtype), O.outlier_kv((hkv, s, 64), g, rate=1e-3).to(dtype)
+    k8, v8, ks, vs = O.quantize_kv_e4m3(k, v)
+    # the reference dequantises to bf16 (its only FP8 test dtype); with fp16 queries the kernels
+    # round the dequantised elements to fp16, the type the MMA runs in
+    kd = (k8.float() * ks.view(-1, 1, 1)).to(dtype)
+    vd = (v8.float() * vs.view(-1, 1, 1)).to(dtype)
+    ref = O.attend_one_sequence(q, kd, vd)
+    if dtype == torch.bfloat16:
+        assert torch.equal(ref, O.attend_one_sequence_e4m3(q, k8, v8, ks, vs))
+    dev = [t.to(DEV) for t in (q, k8, v8, ks, vs)]
+    out = G.gqa_decode_attention_fp8(*dev)
+    _check(G, out, ref)
+    if s >= 4096:
+        for kw in (dict(num_splits=5), dict(reduction="python", num_splits=3)):
+            _check(G, G.gqa_decode_attention_fp8(*dev, **kw), ref)
+
+
+@pytest.mark.parametrize("layout,page_size", [("padded", 0), ("paged_hnd", 16), ("paged_nhd", 64), ("paged_hnd", 256)])
+def test_fp8_head_dim_64_batches(G, layout, page_size):
+    """Ragged batch of E4M3 caches with head_dim 64, padded and in pages shorter and longer than
+    the 128-key tile: against the oracle sequence by sequence, and bit-equal across layouts."""
+    lens = [1, 300, 0, 5000, 129, 2048]
+    b, hq, hkv, d, smax = len(lens), 16, 4, 64, 5120
+    g = torch.Generator().manual_seed(5)
+    q = O.randn_bf16((b, hq, d), g)
+    k = O.outlier_kv((b, hkv, smax, d), g, rate=1e-3)
+    v = O.outlier_kv((b, hkv, smax, d), g, rate=1e-3)
+    k8, v8, ks, vs = O.quantize_kv_e4m3(k.view(b * hkv, smax, d), v.view(b * hkv, smax, d))
+    k8, v8, ks, vs = k8.view(b, hkv, smax, d), v8.view(b, hkv, smax, d), ks.view(b, hkv), vs.view(b, hkv)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    padded = G.gqa_decode_attention_batched(q.to(DEV), k8.to(DEV), v8.to(DEV), sl, k_scale=ks.to(DEV),
+                                            v_scale=vs.to(DEV))
+    assert G.read_status() == 0
+    for i, l in enumerate(lens):
+        if l == 0:
+            assert bool((padded[i] == 0).all())
+            continue
+        ref = O.attend_one_sequence_e4m3(q[i], k8[i, :, :l], v8[i, :, :l], ks[i], vs[i])
+        _check(G, padded[i], ref)
+    if layout == "padded":
+        return
+    need = [(l + page_size - 1) // page_size for l in lens]
+    pages = sum(need) + 3
+    order = torch.randperm(pages, generator=g)
+    table = torch.zeros(b, max(need), dtype=torch.int32)
+    hnd = layout == "paged_hnd"
+    shape = (pages, hkv, page_size, d) if hnd else (pages, page_size, hkv, d)
+    pk = torch.zeros(shape, dtype=torch.uint8)
+    pv = torch.zeros(shape, dtype=torch.uint8)
+    at = 0
+    for i, l in enumerate(lens):
+        for p in range(need[i]):
+            pg = int(order[at]); at += 1
+            table[i, p] = pg
+            n = min(page_size, l - p * page_size)
+            src_k = k8[i, :, p * page_size:p * page_size + n].view(torch.uint8)
+            src_v = v8[i, :, p * page_size:p * page_size + n].view(torch.uint8)
+            if hnd:
+                pk[pg, :, :n], pv[pg, :, :n] = src_k, src_v
+            else:
+                pk[pg, :n], pv[pg, :n] = src_k.transpose(0, 1), src_v.transpose(0, 1)
+    out = G.gqa_decode_attention_batched(
+        q.to(DEV), pk.view(torch.float8_e4m3fn).to(DEV), pv.view(torch.float8_e4m3fn).to(DEV), sl,
+        k_scale=ks.to(DEV), v_scale=vs.to(DEV), layout=layout, block_table=table.to(DEV))
+    assert G.read_status() == 0
+    assert torch.equal(out, padded)
