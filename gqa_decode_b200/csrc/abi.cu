@@ -139,7 +139,7 @@ static int group_overhead_for(int head_dim, int kv_dtype) {
 constexpr int kFp8Warps = 8;
 constexpr int kFp8Tile = 256;
 static int tile_rows_for(int head_dim, int kv_dtype) {
-  if (kv_dtype == GQA_DTYPE_E4M3) return head_dim == 128 ? kFp8Tile : head_dim == 64 ? 128 : 0;
+  if (kv_dtype == GQA_DTYPE_E4M3) return (head_dim == 128 || head_dim == 64) ? kFp8Tile : 0;
   if (head_dim == 256) return 64;
   if (head_dim == 128) return 64;
   if (head_dim == 64) return 128;

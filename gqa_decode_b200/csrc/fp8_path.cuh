@@ -271,15 +271,15 @@ struct KvFp8Traits {
 // like dequantize_kv_fp8 (gqa_decode/fp8_utils.py:54-55: float32(code) * scale, rounded to the
 // 16-bit type - K and V alike) into a scratch of its own behind the stage's raw bytes, laid out
 // as the 128-byte-swizzled rows the 16-bit consumer reads, and then runs that consumer on it.
-// Tiles of 128 keys: [128 x 64 B] for K and for V, unswizzled.
+// Tiles of 256 keys: [256 x 64 B] for K and for V, unswizzled; eight consumer warps.
 // ---------------------------------------------------------------------------
-template <typename T16_, bool UPPER_>
+template <typename T16_, bool UPPER_, int TILE_ = 256, int WARPS_ = 8>
 struct KvFp8Dim64Traits {
   using Q = T16_;
   static constexpr int D = 64;
-  static constexpr int TILE = 128;
+  static constexpr int TILE = TILE_;
   static constexpr bool UPPER = UPPER_;
-  static constexpr int kWarps = 4;
+  static constexpr int kWarps = WARPS_;  // 32 keys (two blocks) per warp and tile
   static constexpr int kGroups = 1;
   static constexpr bool kFp8 = true;
   static constexpr int kBoxesPerTensor = 1;
