@@ -886,7 +886,7 @@ def main():
     # ---- the other workloads, briefly, at the same N
     others = {}
     if not args.no_others:
-        todo = [(n, {}) for n in WORKLOADS if n not in (args.workload, "paged")]
+        todo = [(n, {}) for n in WORKLOADS if n != args.workload]
         if world > 1:
             todo.append(("headshard", {"gather": "fused"}))
         for name, kw in todo:
